@@ -1,0 +1,341 @@
+// fp8_gemm_sm100.cu — libfp8gemm.so for NVIDIA B200 (sm_100a).
+//
+//   C[M,N] = alpha * A[M,K] . B[N,K]^T     A, B: e4m3 codes, K contiguous; C: fp16 or bf16
+//
+// Drop-in for goml's libs/fp8_gemm.cu:308-355 (same three exported symbols,
+// same argument meaning and return convention), rebuilt around the Blackwell
+// data path instead of mma.sync:
+//
+//   TMA (128-byte swizzle) -> 4-stage shared-memory ring under mbarriers
+//     -> one thread issues tcgen05.mma kind::f8f6f4 (M128 x N256 x K32), FP32
+//        accumulators in tensor memory, double buffered (2 x 256 columns)
+//     -> 4 epilogue warps read TMEM (tcgen05.ld), scale, convert and store with
+//        128-bit stores while the next tile's main loop already runs.
+//
+// One persistent CTA per SM walks output tiles in an order that keeps a band of
+// A rows and a few B panels resident in L2.  No multicast, no clusters.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fp8_gemm.h"
+#include "sm100_ptx.cuh"
+#include "tmap.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;          // rows of C per tile (= TMEM lanes)
+constexpr int BN = 256;          // columns of C per tile (= TMEM columns per buffer)
+constexpr int BK = 128;          // K bytes per pipeline stage (one 128-byte swizzle span)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int TMEM_COLS = 512;    // 2 accumulator buffers x 256 fp32 columns
+constexpr int GROUP_M = 16;       // tile-order band height (in tiles)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+enum : uint32_t {
+    ST_OK = 0,
+    ST_TIMEOUT_PRODUCER = 0x101,
+    ST_TIMEOUT_MMA = 0x102,
+    ST_TIMEOUT_EPILOGUE = 0x103,
+};
+
+__device__ uint32_t g_gemm_status = 0;  // first non-zero code any CTA reported (per device)
+
+struct GemmParams {
+    int M, N, K;
+    void* C;
+    float alpha;
+    const float* scale_a;
+    const float* scale_b;
+    int out_bf16;
+    int m_tiles, n_tiles, k_blocks;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
+    const int per_group = GROUP_M * n_tiles;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(m_tiles - first_m, GROUP_M);
+    const int r = t - g * per_group;
+    tm = first_m + r % gsize;
+    tn = r / gsize;
+}
+
+__device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
+    if (bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // operand tiles need 1024-byte alignment (swizzle atom = 8 rows x 128 B)
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    const uint32_t bar_full = bars;
+    const uint32_t bar_empty = bars + 8 * STAGES;
+    const uint32_t bar_tfull = bars + 16 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 16 * STAGES + 32);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 1;  // "previous phase complete": the ring starts empty
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                    const uint32_t fb = bar_full + 8 * stage;
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    mbar_arrive_expect_tx(fb, STAGE_BYTES);
+                    tma_load_2d(sa, &tmap_a, fb, kb * BK, tm * BM);
+                    tma_load_2d(sa + A_BYTES, &tmap_b, fb, kb * BK, tn * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_e4m3_f32(BM, BN, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t tphase[2] = {1, 1};  // both accumulator buffers start free
+            int buf = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(bar_tempty + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_MMA)) break;
+                tphase[buf] ^= 1;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint64_t adesc = kmajor_desc_sw128(sa);
+                    const uint64_t bdesc = kmajor_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; k++) {
+                        // +32 bytes along K inside the swizzle span = +2 in the address field
+                        mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) mma_commit(bar_tfull + 8 * buf);  // accumulator complete
+                buf ^= 1;
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int row_in_tile = quad * 32 + lane;  // TMEM lane = row of the tile
+        float alpha = p.alpha;
+        if (p.scale_a) alpha *= __ldg(p.scale_a);
+        if (p.scale_b) alpha *= __ldg(p.scale_b);
+        const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        uint32_t tphase[2] = {0, 0};
+        int buf = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            int tm, tn;
+            tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+            if (!mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_EPILOGUE)) break;
+            tphase[buf] ^= 1;
+            tc_fence_after();
+            const int row = tm * BM + row_in_tile;
+            const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
+            uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                const int col0 = tn * BN + c * 32;
+                if (col0 >= p.N) break;  // uniform across the CTA
+                uint32_t acc[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, acc);
+                tmem_ld_wait();
+                if (row < p.M) {
+                    if (vec_ok && col0 + 32 <= p.N) {
+                        uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            uint4 o;
+                            o.x = pack_out(__uint_as_float(acc[8 * v + 0]) * alpha, __uint_as_float(acc[8 * v + 1]) * alpha, p.out_bf16);
+                            o.y = pack_out(__uint_as_float(acc[8 * v + 2]) * alpha, __uint_as_float(acc[8 * v + 3]) * alpha, p.out_bf16);
+                            o.z = pack_out(__uint_as_float(acc[8 * v + 4]) * alpha, __uint_as_float(acc[8 * v + 5]) * alpha, p.out_bf16);
+                            o.w = pack_out(__uint_as_float(acc[8 * v + 6]) * alpha, __uint_as_float(acc[8 * v + 7]) * alpha, p.out_bf16);
+                            dst[v] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (col0 + j < p.N) {
+                                const float f = __uint_as_float(acc[j]) * alpha;
+                                uint16_t bits;
+                                if (p.out_bf16) { __nv_bfloat16 h = __float2bfloat16_rn(f); bits = *reinterpret_cast<uint16_t*>(&h); }
+                                else { __half h = __float2half_rn(f); bits = *reinterpret_cast<uint16_t*>(&h); }
+                                crow[col0 + j] = bits;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+            buf ^= 1;
+        }
+    }
+
+    // ------------------------------------------------------------- teardown
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    const uint32_t code = *abort_flag;
+    if (code != 0) {
+        // a wait ran out: report, then give copies already in flight a bounded
+        // time to land before shared memory and TMEM are released
+        if (threadIdx.x == 0) atomicCAS(&g_gemm_status, 0u, code);
+        for (int i = 0; i < 200; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+
+struct DeviceState {
+    bool ready = false;
+    int num_sms = 0;
+};
+constexpr int MAX_DEVICES = 64;
+DeviceState g_dev[MAX_DEVICES];
+
+int launch(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* sa, const float* sb,
+           int out_bf16, cudaStream_t stream) {
+    if (M < 0 || N < 0 || K < 0) return (int)cudaErrorInvalidValue;
+    if (M == 0 || N == 0) return 0;
+    if (!A || !B || !C) return (int)cudaErrorInvalidValue;
+    if (K == 0 || (K % 16) != 0) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+        (reinterpret_cast<uintptr_t>(C) & 1))
+        return (int)cudaErrorInvalidValue;
+
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        int major = 0, sms = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return (int)e;
+        if (major != 10) return (int)cudaErrorNoKernelImageForDevice;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      SMEM_BYTES)) != cudaSuccess)
+            return (int)e;
+        st.num_sms = sms;
+        st.ready = true;
+    }
+
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K; p.C = C;
+    p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
+    p.m_tiles = (M + BM - 1) / BM;
+    p.n_tiles = (N + BN - 1) / BN;
+    p.k_blocks = (K + BK - 1) / BK;
+
+    CUtensorMap ta, tb;
+    if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B))
+        return (int)cudaErrorInvalidValue;
+
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    const int grid = (int)(tiles < st.num_sms ? tiles : st.num_sms);
+    fp8_gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp8_gemm(int M, int N, int K, const void* A, const void* B, void* C, int mode, void* stream) {
+    (void)mode;  // 0 and 1 name the reference's two mma.sync variants; one tcgen05 kernel serves both
+    return launch(M, N, K, A, B, C, 1.0f, nullptr, nullptr, 0, (cudaStream_t)stream);
+}
+
+int fp8_gemm_original(int M, int N, int K, const void* A, const void* B, void* C, void* stream) {
+    return fp8_gemm(M, N, K, A, B, C, 0, stream);
+}
+
+int fp8_gemm_singlesync(int M, int N, int K, const void* A, const void* B, void* C, void* stream) {
+    return fp8_gemm(M, N, K, A, B, C, 1, stream);
+}
+
+int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* scale_a,
+                    const float* scale_b, int out_dtype, void* stream) {
+    if (out_dtype != FP8_GEMM_OUT_FP16 && out_dtype != FP8_GEMM_OUT_BF16) return (int)cudaErrorInvalidValue;
+    return launch(M, N, K, A, B, C, alpha, scale_a, scale_b, out_dtype == FP8_GEMM_OUT_BF16, (cudaStream_t)stream);
+}
+
+int fp8_gemm_device_status(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return -(int)e;
+    uint32_t code = 0, zero = 0;
+    e = cudaMemcpyFromSymbol(&code, g_gemm_status, sizeof(code));
+    if (e != cudaSuccess) return -(int)e;
+    if (code != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero));
+    return (int)code;
+}
+
+const char* fp8_gemm_version(void) { return "1.0.0+tcgen05-sm100a"; }
+
+}  // extern "C"

@@ -1,0 +1,86 @@
+"""Host binding of libfp8gemm.so, mirroring goml's backend/cuda/fp8_gemm.go.
+
+``FP8GEMM(M, N, K, A, B, C, mode, stream)`` has the argument meaning of
+``cuda.FP8GEMM`` (backend/cuda/fp8_gemm.go:52-62): raw device pointers as
+integers, ``mode`` 0/1, ``stream`` a CUDA stream handle or 0, and a non-zero
+return code raised as ``"fp8_gemm: CUDA error %d"``.  ``FP8GEMMScaled`` binds
+the additive extension (dequantising alpha, BF16 output).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+from . import loader
+
+ModeOriginal = 0
+ModeSinglesync = 1
+OutFP16 = 0
+OutBF16 = 1
+
+
+class FP8GEMMError(RuntimeError):
+    pass
+
+
+_state = {"lib": None, "err": None}
+_once = threading.Lock()
+
+
+def _init():
+    """sync.Once-style load of libfp8gemm.so (backend/cuda/fp8_gemm.go:27-41)."""
+    with _once:
+        if _state["lib"] is None and _state["err"] is None:
+            try:
+                lib = loader.dlopen(loader.resolve_lib("libfp8gemm.so"), global_symbols=True)
+                i, p, f = C.c_int, C.c_void_p, C.c_float
+                lib.fp8_gemm.restype = i
+                lib.fp8_gemm.argtypes = [i, i, i, p, p, p, i, p]
+                for name in ("fp8_gemm_original", "fp8_gemm_singlesync"):
+                    fn = getattr(lib, name)
+                    fn.restype = i
+                    fn.argtypes = [i, i, i, p, p, p, p]
+                lib.fp8_gemm_scaled.restype = i
+                lib.fp8_gemm_scaled.argtypes = [i, i, i, p, p, p, f, p, p, i, p]
+                lib.fp8_gemm_device_status.restype = i
+                lib.fp8_gemm_version.restype = C.c_char_p
+                _state["lib"] = lib
+            except OSError as e:
+                _state["err"] = e
+    if _state["err"] is not None:
+        raise _state["err"]
+    return _state["lib"]
+
+
+def FP8GEMM(M: int, N: int, K: int, A: int, B: int, Cptr: int, mode: int = ModeSinglesync, stream: int = 0) -> None:
+    """C[M,N] (fp16) = A[M,K] x B[N,K]^T on e4m3 device buffers."""
+    rc = _init().fp8_gemm(M, N, K, A, B, Cptr, mode, stream)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm: CUDA error {rc}")
+
+
+def FP8GEMMOriginal(M, N, K, A, B, Cptr, stream=0) -> None:
+    rc = _init().fp8_gemm_original(M, N, K, A, B, Cptr, stream)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm: CUDA error {rc}")
+
+
+def FP8GEMMSinglesync(M, N, K, A, B, Cptr, stream=0) -> None:
+    rc = _init().fp8_gemm_singlesync(M, N, K, A, B, Cptr, stream)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm: CUDA error {rc}")
+
+
+def FP8GEMMScaled(M, N, K, A, B, Cptr, alpha=1.0, scale_a=0, scale_b=0, out_dtype=OutBF16, stream=0) -> None:
+    """C = alpha * (*scale_a) * (*scale_b) * A x B^T; scale pointers are device pointers or 0."""
+    rc = _init().fp8_gemm_scaled(M, N, K, A, B, Cptr, alpha, scale_a or None, scale_b or None, out_dtype, stream)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_scaled: CUDA error {rc}")
+
+
+def device_status() -> int:
+    return _init().fp8_gemm_device_status()
+
+
+def version() -> str:
+    return _init().fp8_gemm_version().decode()

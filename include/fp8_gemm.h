@@ -1,0 +1,71 @@
+/*
+ * fp8_gemm.h — C ABI of libfp8gemm.so, the FP8 (e4m3) GEMM
+ *     C[M,N] = alpha * A[M,K] . B[N,K]^T          ("TN": both operands K-contiguous)
+ * implemented for NVIDIA B200 (sm_100a) with tcgen05 tensor-core MMA.
+ *
+ * The first three entry points replace, symbol for symbol, the ones goml binds
+ * with purego in backend/cuda/fp8_gemm.go:27-62 and that its libs/fp8_gemm.cu:315-353
+ * defines.  Conventions kept from there:
+ *   - every pointer is a device pointer owned by the caller; nothing is allocated
+ *     or freed; the call is asynchronous on `stream` (NULL = default stream) and
+ *     never synchronises the host;
+ *   - the return value is a cudaError_t as int, 0 = success;
+ *   - A is [M,K] row-major u8 (e4m3 codes), B is [N,K] row-major u8 (i.e. the
+ *     [out,in] weight layout of nn/linear.go:14), C is [M,N] row-major;
+ *   - K must be a multiple of 16 and A, B 16-byte aligned (libs/fp8_gemm.cu:83-103
+ *     loads 16-byte units); violations return cudaErrorInvalidValue (1) here
+ *     instead of reading out of bounds;
+ *   - the calling thread's current device is used; per-device state is kept
+ *     per device and the current device is never changed.
+ * Deliberate differences: accumulation is FP32 in tensor memory (the reference
+ * accumulates in FP16 and overflows above 65504); an odd N is handled (the
+ * reference drops the last column, libs/fp8_gemm.cu:122-125).
+ */
+#ifndef GOML_FP8_GEMM_H_
+#define GOML_FP8_GEMM_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__) || defined(__clang__)
+#define FP8GEMM_API __attribute__((visibility("default")))
+#else
+#define FP8GEMM_API
+#endif
+
+/* Replaces fp8_gemm of libs/fp8_gemm.cu:315-340.  C is FP16, alpha = 1.
+ * mode: 0 or 1 (the reference's "original"/"singlesync" kernels); any other
+ * value is treated as 1.  Both modes run the same sm_100a kernel. */
+FP8GEMM_API int fp8_gemm(int M, int N, int K, const void* A, const void* B, void* C, int mode, void* stream);
+
+/* Replaces fp8_gemm_original of libs/fp8_gemm.cu:343-347. */
+FP8GEMM_API int fp8_gemm_original(int M, int N, int K, const void* A, const void* B, void* C, void* stream);
+
+/* Replaces fp8_gemm_singlesync of libs/fp8_gemm.cu:349-353. */
+FP8GEMM_API int fp8_gemm_singlesync(int M, int N, int K, const void* A, const void* B, void* C, void* stream);
+
+/* Additive extension (no counterpart in the reference ABI, which cannot express
+ * per-tensor dequantisation or a BF16 result):
+ *   C = (alpha * (*scale_a) * (*scale_b)) * A . B^T
+ * scale_a / scale_b are optional DEVICE pointers to one float each (the scales a
+ * quantiser wrote; NULL = 1), read by the kernel so no host round trip is needed.
+ * out_dtype: 0 = FP16, 1 = BF16. */
+#define FP8_GEMM_OUT_FP16 0
+#define FP8_GEMM_OUT_BF16 1
+FP8GEMM_API int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
+                                const float* scale_a, const float* scale_b, int out_dtype, void* stream);
+
+/* Additive: device-side status of the current device.  The kernels bound every
+ * wait; if a wait ever runs out they record a non-zero code here and exit
+ * cleanly.  This call synchronises the device and returns (and clears) the
+ * code; 0 = no kernel reported a problem.  Negative = CUDA error code negated. */
+FP8GEMM_API int fp8_gemm_device_status(void);
+
+/* Additive: static version string. */
+FP8GEMM_API const char* fp8_gemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GOML_FP8_GEMM_H_ */
