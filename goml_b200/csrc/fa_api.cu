@@ -1,0 +1,165 @@
+// fa_api.cu — context lifecycle, argument validation and the C entry points of
+// libfa_sm120.so (the ABI of goml's libs/fa_sm120/src/fa_ctx.cu:55-235).
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/fa_sm120.h"
+#include "fa_fwd_sm100.h"
+
+struct fa_ctx {
+    int device;
+    int cc_major, cc_minor;
+    bool arch_ok;
+    char last_err[256];
+};
+
+namespace {
+
+void set_err(fa_ctx_t* c, const char* fmt, const char* a = "", const char* b = "") {
+    if (c) snprintf(c->last_err, sizeof(c->last_err), fmt, a, b);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Checks shared by every forward entry.  `who` prefixes messages.
+fa_status_t validate(fa_ctx_t* c, const char* who, const void* q, const void* k, const void* v, const void* o,
+                     int bh, int sl, int hd, int causal, int window) {
+    if (!c->arch_ok) { set_err(c, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
+    if (!q || !k || !v || !o) { set_err(c, "%s: null pointer in q/k/v/o", who); return FA_ERR_INVALID_ARG; }
+    if (bh <= 0 || sl <= 0) { set_err(c, "%s: bh/sl must be > 0", who); return FA_ERR_INVALID_ARG; }
+    if (hd != 64 && hd != 128) { set_err(c, "%s: head_dim must be 64 or 128", who); return FA_ERR_UNSUPPORTED_HD; }
+    if (window < 0 || window > sl) { set_err(c, "%s: window must be in [0, seq_len]", who); return FA_ERR_INVALID_ARG; }
+    if (causal != 0 && causal != 1) { set_err(c, "%s: causal must be 0 or 1", who); return FA_ERR_INVALID_ARG; }
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) {
+        set_err(c, "%s: q/k/v/o must be 16-byte aligned", who);
+        return FA_ERR_INVALID_ARG;
+    }
+    if (fa_dispatch_select(bh, sl, hd, causal, window) == FA_KERNEL_NONE) {
+        set_err(c, "%s: no kernel matches this configuration", who);
+        return FA_ERR_UNSUPPORTED_SHAPE;
+    }
+    return FA_OK;
+}
+
+fa_status_t run(fa_ctx_t* c, const char* who, const fa_sm100::LaunchArgs& a) {
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) { set_err(c, "%s: cudaGetDevice: %s", who, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    if (cur != c->device) {
+        // one context serves the device it was created on; the caller keeps that device current
+        set_err(c, "%s: the calling thread's current device differs from the context's device", who);
+        return FA_ERR_INVALID_ARG;
+    }
+    e = fa_sm100::launch(a);
+    if (e != cudaSuccess) { set_err(c, "%s: launch: %s", who, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    return FA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+fa_status_t fa_create(fa_ctx_t** ctx_out) {
+    if (!ctx_out) return FA_ERR_INVALID_ARG;
+    *ctx_out = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return FA_ERR_CUDA;
+    fa_ctx_t* c = new (std::nothrow) fa_ctx_t();
+    if (!c) return FA_ERR_OOM;
+    c->device = dev;
+    c->last_err[0] = '\0';
+    if (cudaDeviceGetAttribute(&c->cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&c->cc_minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) {
+        delete c;
+        return FA_ERR_CUDA;
+    }
+    c->arch_ok = (c->cc_major == 10);
+    *ctx_out = c;  // returned even on an unsupported GPU so the caller can read the reason
+    if (!c->arch_ok) {
+        snprintf(c->last_err, sizeof(c->last_err),
+                 "GPU compute capability %d.%d is not sm_100a (need 10.x).", c->cc_major, c->cc_minor);
+        return FA_ERR_UNSUPPORTED_ARCH;
+    }
+    return FA_OK;
+}
+
+fa_status_t fa_destroy(fa_ctx_t* ctx) {
+    delete ctx;
+    return FA_OK;
+}
+
+const char* fa_version(void) { return "1.0.0+tcgen05-sm100a"; }
+
+const char* fa_status_str(fa_status_t s) {
+    switch (s) {
+        case FA_OK: return "OK";
+        case FA_ERR_INVALID_ARG: return "invalid argument";
+        case FA_ERR_UNSUPPORTED_ARCH: return "unsupported GPU arch (need sm_100a)";
+        case FA_ERR_UNSUPPORTED_HD: return "unsupported head_dim (need 64 or 128)";
+        case FA_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+        case FA_ERR_CUDA: return "CUDA runtime error";
+        case FA_ERR_OOM: return "out of memory";
+        case FA_ERR_INTERNAL: return "internal error";
+    }
+    return "unknown";
+}
+
+const char* fa_last_cuda_error(fa_ctx_t* ctx) { return ctx ? ctx->last_err : ""; }
+
+fa_status_t fa_forward_train(fa_ctx_t* ctx, const void* q, const void* k, const void* v, void* o, void* l_out,
+                             int bh, int sl, int hd, int causal, int window, float scale, fa_stream_t stream) {
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    fa_status_t s = validate(ctx, "fa_forward_train", q, k, v, o, bh, sl, hd, causal, window);
+    if (s != FA_OK) return s;
+    fa_sm100::LaunchArgs a{};
+    a.q = q; a.k = k; a.v = v; a.o = o; a.lse = static_cast<float*>(l_out);
+    a.bh = bh; a.sl = sl; a.hd = hd; a.causal = causal; a.window = window;
+    a.scale = scale; a.v_descale = 1.0f;
+    a.stream = reinterpret_cast<cudaStream_t>(stream);
+    return run(ctx, "fa_forward_train", a);
+}
+
+fa_status_t fa_forward(fa_ctx_t* ctx, const void* q, const void* k, const void* v, void* o, int bh, int sl, int hd,
+                       int causal, int window, float scale, fa_stream_t stream) {
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    fa_status_t s = validate(ctx, "fa_forward", q, k, v, o, bh, sl, hd, causal, window);
+    if (s != FA_OK) return s;
+    fa_sm100::LaunchArgs a{};
+    a.q = q; a.k = k; a.v = v; a.o = o; a.lse = nullptr;
+    a.bh = bh; a.sl = sl; a.hd = hd; a.causal = causal; a.window = window;
+    a.scale = scale; a.v_descale = 1.0f;
+    a.stream = reinterpret_cast<cudaStream_t>(stream);
+    return run(ctx, "fa_forward", a);
+}
+
+fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* g) {
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    if (!g) { set_err(ctx, "%s: null argument block", "fa_forward_ex"); return FA_ERR_INVALID_ARG; }
+    fa_status_t s = validate(ctx, "fa_forward_ex", g->q, g->k, g->v, g->o, g->batch_heads, g->seq_len, g->head_dim,
+                             g->causal, g->window);
+    if (s != FA_OK) return s;
+    fa_sm100::LaunchArgs a{};
+    a.q = g->q; a.k = g->k; a.v = g->v; a.o = g->o; a.lse = static_cast<float*>(g->l_out);
+    a.bh = g->batch_heads; a.sl = g->seq_len; a.hd = g->head_dim; a.causal = g->causal; a.window = g->window;
+    a.scale = g->scale; a.v_descale = (g->v_descale == 0.0f) ? 1.0f : g->v_descale;
+    a.scale_q_dev = g->scale_q_dev; a.scale_k_dev = g->scale_k_dev; a.scale_v_dev = g->scale_v_dev;
+    a.stream = reinterpret_cast<cudaStream_t>(g->stream);
+    return run(ctx, "fa_forward_ex", a);
+}
+
+fa_status_t fa_device_status(fa_ctx_t* ctx) {
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    const int code = fa_sm100::device_status();
+    if (code == 0) return FA_OK;
+    if (code < 0) {
+        set_err(ctx, "%s: %s", "fa_device_status", cudaGetErrorString(static_cast<cudaError_t>(-code)));
+        return FA_ERR_CUDA;
+    }
+    snprintf(ctx->last_err, sizeof(ctx->last_err), "a kernel wait ran out (device status 0x%x)", code);
+    return FA_ERR_INTERNAL;
+}
+
+}  // extern "C"

@@ -1,0 +1,32 @@
+// fa_fwd_sm100.h — internal launch interface between the C-ABI layer (fa_api.cu)
+// and the sm_100a attention kernels (fa_fwd_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa_sm100 {
+
+struct LaunchArgs {
+    const void* q;      // [bh, sl, hd] e4m3
+    const void* k;
+    const void* v;
+    void* o;            // [bh, sl, hd] fp16
+    float* lse;         // [bh, sl] fp32 natural-log LSE, or nullptr
+    int bh, sl, hd;     // hd in {64, 128}
+    int causal, window;
+    float scale;        // softmax_scale * scale_q * scale_k
+    float v_descale;    // multiplies O (1 = output in decoded-V units, as the reference)
+    const float* scale_q_dev = nullptr;  // optional device scalars multiplied into scale / v_descale
+    const float* scale_k_dev = nullptr;
+    const float* scale_v_dev = nullptr;
+    cudaStream_t stream;
+};
+
+// Launches on the calling thread's current device; asynchronous on a.stream.
+cudaError_t launch(const LaunchArgs& a);
+
+// Synchronises the device and returns (and clears) the first non-zero status
+// code a kernel recorded (a wait that ran out), 0 if none, -cudaError on failure.
+int device_status();
+
+}  // namespace fa_sm100

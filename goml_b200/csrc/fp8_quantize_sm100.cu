@@ -1,0 +1,120 @@
+// fp8_quantize_sm100.cu — libfp8quant.so: per-tensor FP32 -> e4m3 quantiser
+// (amax reduction + scale + round-to-nearest-even, saturating conversion).
+// HBM-bound: the amax pass reads 4 B/element, the conversion pass reads 4 B and
+// writes 1 B per element (the second read is served from L2 when the tensor
+// fits).  128-bit loads, one 128-bit store per 16 elements, grid sized to a
+// multiple of the SM count.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fp8_quantize.h"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+__global__ void __launch_bounds__(THREADS) amax_kernel(const float* __restrict__ x, size_t n, float* amax) {
+    const size_t n4 = n / 4;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float m = 0.f;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = __ldg(x4 + i);
+        m = fmaxf(fmaxf(m, fabsf(v.x)), fmaxf(fabsf(v.y), fmaxf(fabsf(v.z), fabsf(v.w))));  // NaN never wins
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) m = fmaxf(m, fabsf(x[n4 * 4 + threadIdx.x]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float wm[THREADS / 32];
+    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < THREADS / 32 ? wm[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        // non-negative floats order like their bit patterns
+        if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+    }
+}
+
+__device__ __forceinline__ uint32_t quant4(float4 v, float inv) {
+    // x * inv (one rounding, no FMA contraction possible), clamp, RN-even satfinite
+    const float a = fminf(fmaxf(__fmul_rn(v.x, inv), -448.f), 448.f);
+    const float b = fminf(fmaxf(__fmul_rn(v.y, inv), -448.f), 448.f);
+    const float c = fminf(fmaxf(__fmul_rn(v.z, inv), -448.f), 448.f);
+    const float d = fminf(fmaxf(__fmul_rn(v.w, inv), -448.f), 448.f);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__global__ void __launch_bounds__(THREADS) quant_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, size_t n,
+                                                        const float* __restrict__ amax_ptr, float* scale_out,
+                                                        float divisor) {
+    const float amax = *amax_ptr;
+    const float scale = (amax > 1e-12f) ? __fdiv_rn(amax, divisor) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const size_t n16 = n / 16;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    uint4* q16 = reinterpret_cast<uint4*>(q);
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const float4 a = __ldg(x4 + 4 * i), b = __ldg(x4 + 4 * i + 1), c = __ldg(x4 + 4 * i + 2), d = __ldg(x4 + 4 * i + 3);
+        q16[i] = make_uint4(quant4(a, inv), quant4(b, inv), quant4(c, inv), quant4(d, inv));
+    }
+    if (blockIdx.x == 0) {
+        for (size_t i = n16 * 16 + threadIdx.x; i < n; i += blockDim.x) {
+            const float v = fminf(fmaxf(__fmul_rn(x[i], inv), -448.f), 448.f);
+            q[i] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) dequant_kernel(const uint8_t* __restrict__ q, __half* __restrict__ out,
+                                                          const float* __restrict__ scale_in, int n) {
+    const float s = *scale_in;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(q[i], __NV_E4M3);
+        out[i] = __float2half_rn(__half2float(__half(hr)) * s);
+    }
+}
+
+int grid_for(size_t work_items) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t blocks = (work_items + THREADS - 1) / THREADS;
+    const size_t cap = (size_t)sms * 8;  // 8 resident CTAs of 256 threads per SM
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp8_quantize_f32(const float* x, uint8_t* q, float* scale_out, float* amax_out, size_t n, int convention,
+                     void* stream) {
+    if (!x || !q || !scale_out || !amax_out) return (int)cudaErrorInvalidValue;
+    if (convention != FP8_QUANT_AMAX_OVER_448 && convention != FP8_QUANT_UNIT) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    if (n > 0) amax_kernel<<<grid_for(n / 4 + 1), THREADS, 0, s>>>(x, n, amax_out);
+    quant_kernel<<<grid_for(n / 16 + 1), THREADS, 0, s>>>(x, q, n, amax_out, scale_out,
+                                                           convention == FP8_QUANT_UNIT ? 1.0f : 448.0f);
+    return (int)cudaGetLastError();
+}
+
+int fp8_dequantize_to_fp16(const void* input_fp8, void* output_fp16, const float* scale_in, int n) {
+    if (!input_fp8 || !output_fp16 || !scale_in || n < 0) return (int)cudaErrorInvalidValue;
+    if (n == 0) return 0;
+    dequant_kernel<<<grid_for((size_t)n), THREADS>>>((const uint8_t*)input_fp8, (__half*)output_fp16, scale_in, n);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

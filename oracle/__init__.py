@@ -48,6 +48,7 @@ def lib() -> C.CDLL:
         L.oracle_e4m3_encode_n.argtypes = [_f32p, _u8p, C.c_size_t]
         L.oracle_quantize_f32.argtypes = [_f32p, _u8p, _f32p, _f32p, C.c_size_t, C.c_int]
         L.oracle_attention_f64.argtypes = [_u8p, _u8p, _u8p, _f64p, _f64p] + [C.c_int] * 5 + [C.c_double] * 2
+        L.oracle_attention_f64_rows.argtypes = [_u8p, _u8p, _u8p, _f64p, _f64p] + [C.c_int] * 5 + [C.c_double] * 2 + [C.c_int] * 2
         L.oracle_attention_f32.argtypes = [_u8p, _u8p, _u8p, _f32p] + [C.c_int] * 5 + [C.c_float, C.c_int]
         L.oracle_gemm_f64.argtypes = [_u8p, _u8p, _f64p, C.c_int, C.c_int, C.c_int, C.c_double]
         L.oracle_gemm_f32.argtypes = [_u8p, _u8p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int]
@@ -109,6 +110,21 @@ def attention_f64(q, k, v, causal=0, window=0, scale=None, v_descale=1.0, want_l
     lib().oracle_attention_f64(_p(q, _u8p), _p(k, _u8p), _p(v, _u8p), _p(o, _f64p),
                                _p(lse, _f64p) if want_lse else None,
                                bh, sl, hd, int(causal), int(window), float(scale), float(v_descale))
+    return o, lse
+
+
+def attention_f64_rows(q, k, v, q_begin, q_end, causal=0, window=0, scale=None, v_descale=1.0):
+    """FP64 attention for query rows [q_begin, q_end) of every head."""
+    q, k, v = _u8(q), _u8(k), _u8(v)
+    bh, sl, hd = q.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(hd)
+    nq = q_end - q_begin
+    o = np.empty((bh, nq, hd), np.float64)
+    lse = np.empty((bh, nq), np.float64)
+    lib().oracle_attention_f64_rows(_p(q, _u8p), _p(k, _u8p), _p(v, _u8p), _p(o, _f64p), _p(lse, _f64p),
+                                    bh, sl, hd, int(causal), int(window), float(scale), float(v_descale),
+                                    int(q_begin), int(q_end))
     return o, lse
 
 

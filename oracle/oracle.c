@@ -312,3 +312,60 @@ ORACLE_API int oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/* Same arithmetic as oracle_attention_f64, restricted to query rows
+ * [q_begin, q_end) of every head (outputs are [bh, q_end-q_begin, hd] and
+ * [bh, q_end-q_begin]).  Used to check full-size problems on a sample of rows. */
+ORACLE_API void oracle_attention_f64_rows(const uint8_t *q, const uint8_t *k, const uint8_t *v,
+                                          double *o, double *lse,
+                                          int bh, int sl, int hd, int causal, int window,
+                                          double scale, double v_descale, int q_begin, int q_end)
+{
+    float lut[256];
+    for (int i = 0; i < 256; i++) lut[i] = oracle_e4m3_decode((uint8_t)i);
+    size_t hs = (size_t)sl * hd;
+    int nq = q_end - q_begin;
+#pragma omp parallel
+    {
+        double *p = (double *)malloc(sizeof(double) * (size_t)sl);
+        double *acc = (double *)malloc(sizeof(double) * (size_t)hd);
+#pragma omp for collapse(2) schedule(dynamic, 4)
+        for (int h = 0; h < bh; h++) {
+            for (int qi = 0; qi < nq; qi++) {
+                const uint8_t *Qh = q + h * hs, *Kh = k + h * hs, *Vh = v + h * hs;
+                int i = q_begin + qi;
+                int j1 = causal ? (i + 1) : sl;
+                int j0 = (window > 0 && i + 1 > window) ? (i - window + 1) : 0;
+                double qrow[256];
+                for (int d = 0; d < hd; d++) qrow[d] = lut[Qh[(size_t)i * hd + d]];
+                double mx = -INFINITY;
+                for (int j = j0; j < j1; j++) {
+                    const uint8_t *kr = Kh + (size_t)j * hd;
+                    double s = 0.0;
+                    for (int d = 0; d < hd; d++) s += qrow[d] * (double)lut[kr[d]];
+                    s *= scale;
+                    p[j] = s;
+                    if (s > mx) mx = s;
+                }
+                double *orow = o + ((size_t)h * nq + qi) * hd;
+                if (j1 <= j0 || isinf(mx)) {
+                    for (int d = 0; d < hd; d++) orow[d] = 0.0;
+                    if (lse) lse[(size_t)h * nq + qi] = -INFINITY;
+                    continue;
+                }
+                double sum = 0.0;
+                for (int j = j0; j < j1; j++) { p[j] = exp(p[j] - mx); sum += p[j]; }
+                for (int d = 0; d < hd; d++) acc[d] = 0.0;
+                for (int j = j0; j < j1; j++) {
+                    const uint8_t *vr = Vh + (size_t)j * hd;
+                    double pj = p[j];
+                    for (int d = 0; d < hd; d++) acc[d] += pj * (double)lut[vr[d]];
+                }
+                double inv = v_descale / sum;
+                for (int d = 0; d < hd; d++) orow[d] = acc[d] * inv;
+                if (lse) lse[(size_t)h * nq + qi] = mx + log(sum);
+            }
+        }
+        free(p); free(acc);
+    }
+}

@@ -1,0 +1,121 @@
+"""FP8 GEMM parity on the GPU, through the C ABI, against the oracle.
+
+Tolerances.  The reference's own gate (libs/fp8_gemm_bench.cu:120-129) is
+|gpu-ref| <= max(1.0, 0.05|ref|).  The bar used here for seeded N(0,1) data:
+max-abs error <= 2e-2 and mean relative error <= 1e-2, both measured on C
+normalised by RMS(C_ref) — at 4096^3 the un-normalised products have RMS ~ 64
+where one bf16 step is 0.25, so an absolute 2e-2 is below the output format's
+resolution.  In addition the result must equal the oracle's fp64 result rounded
+to the output type up to one unit in the last place (accumulation is fp32).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from tests.gpu_util import dev_u8, run_gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def check(got, ref64, bf16):
+    rms = np.sqrt(np.mean(ref64 ** 2))
+    maxabs, meanrel = O.error_stats(got / rms, ref64 / rms)
+    assert maxabs <= 2e-2, maxabs
+    assert meanrel <= 1e-2, meanrel
+    # within one ulp of the correctly rounded result
+    ulp = np.abs(ref64) * (2.0 ** -7 if bf16 else 2.0 ** -10) + 1e-3 * rms  # floor: fp32 accumulation noise near 0
+    assert np.all(np.abs(got - ref64) <= ulp)
+
+
+@pytest.mark.parametrize("entry", ["gemm", "original", "singlesync"])
+@pytest.mark.parametrize("n", [128, 256, 512])
+def test_reference_selfcheck_shapes(cuda, built_libs, golden, entry, n):
+    # libs/fp8_gemm_bench.cu:81-141: srand(42) inputs, 128^3/256^3/512^3, fp16 out
+    a, b = O.harness_gemm_inputs(n, n, n)
+    got = run_gemm(a, b, bf16=False, entry=entry)
+    ref = O.gemm_f32(a, b, parallel=True).astype(np.float64)
+    if n == 128:
+        assert np.array_equal(ref, golden["gemm_128_ref"].astype(np.float64))
+    assert np.all(np.abs(got - ref) <= np.maximum(1.0, 0.05 * np.abs(ref)))       # the reference's gate
+    assert np.array_equal(got, O.round_fp16(ref).astype(np.float64))             # and in fact exact
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (1024, 1024, 1024), (384, 640, 2048)])
+@pytest.mark.parametrize("bf16", [True, False])
+def test_seeded_normal_amax448(cuda, built_libs, M, N, K, bf16):
+    # config: A, B ~ N(0,1) quantised per tensor with scale = amax/448; C = sa*sb * A.B^T
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (M, K), config=f"gemm{M}x{N}x{K}"))
+    b, sb, _ = O.quantize_f32(O.seeded_normal("B", (N, K), config=f"gemm{M}x{N}x{K}"))
+    alpha = float(sa) * float(sb)
+    got = run_gemm(a, b, alpha=alpha, bf16=bf16)
+    check(got, O.gemm_f64(a, b, alpha), bf16)
+
+
+def test_device_scale_pointers(cuda, built_libs):
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (128, 256), config="ptr"))
+    b, sb, _ = O.quantize_f32(O.seeded_normal("B", (256, 256), config="ptr"))
+    s = torch.tensor([float(sa), float(sb)], dtype=torch.float32, device="cuda")
+    got = run_gemm(a, b, alpha=1.0, scale_ptrs=(s.data_ptr(), s.data_ptr() + 4))
+    check(got, O.gemm_f64(a, b, float(np.float32(sa) * np.float32(sb))), True)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 16), (16, 8192, 256), (129, 257, 160), (300, 520, 144), (127, 255, 4096),
+                                    (130, 7, 48), (5, 1000, 16)])
+def test_ragged_and_tiny_shapes(cuda, built_libs, M, N, K):
+    rng = np.random.default_rng(M * 1000 + N)
+    a = rng.integers(0, 0x7F, (M, K), dtype=np.uint8) | (rng.integers(0, 2, (M, K), dtype=np.uint8) << 7)
+    b = rng.integers(0, 0x60, (N, K), dtype=np.uint8) | (rng.integers(0, 2, (N, K), dtype=np.uint8) << 7)
+    alpha = 2.0 ** -10
+    got = run_gemm(a, b, alpha=alpha, bf16=True)
+    check(got, O.gemm_f64(a, b, alpha), True)
+
+
+def test_output_outside_the_matrix_is_untouched(cuda, built_libs):
+    from goml_b200 import fp8_gemm as G
+    M, N, K = 100, 72, 64
+    a, b = O.harness_gemm_inputs(M, N, K)
+    ad, bd = dev_u8(a), dev_u8(b)
+    buf = torch.full((M * N + 512,), 7.0, dtype=torch.float16, device="cuda")
+    G.FP8GEMM(M, N, K, ad.data_ptr(), bd.data_ptr(), buf.data_ptr() + 512, 1, 0)   # C starts 256 elements in
+    torch.cuda.synchronize()
+    assert torch.all(buf[:256] == 7.0) and torch.all(buf[256 + M * N:] == 7.0)
+    ref = O.round_fp16(O.gemm_f32(a, b)).astype(np.float64)
+    assert np.array_equal(buf[256:256 + M * N].double().cpu().numpy().reshape(M, N), ref)
+
+
+def test_fp32_accumulation_does_not_overflow_like_fp16(cuda, built_libs):
+    # all codes 0x7E (448): 448*448*K overflows an fp16 accumulator; alpha brings the result into range
+    K = 256
+    a = np.full((128, K), 0x7E, np.uint8)
+    b = np.full((256, K), 0x7E, np.uint8)
+    got = run_gemm(a, b, alpha=2.0 ** -16, bf16=True)
+    assert np.allclose(got, 448.0 * 448.0 * K * 2.0 ** -16, rtol=2 ** -8)
+
+
+def test_config2_full_size_on_sampled_rows(cuda, built_libs):
+    # M=N=K=4096, bf16 out scaled by sa*sb; oracle on 48 sampled rows (all columns)
+    from goml_b200 import fp8_gemm as G
+    n = 4096
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (n, n), config="C2"))
+    b, sb, _ = O.quantize_f32(O.seeded_normal("B", (n, n), config="C2"))
+    alpha = float(sa) * float(sb)
+    ad, bd = dev_u8(a), dev_u8(b)
+    c = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+    G.FP8GEMMScaled(n, n, n, ad.data_ptr(), bd.data_ptr(), c.data_ptr(), alpha, 0, 0, G.OutBF16, 0)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    rows = np.unique(np.concatenate([[0, 127, 128, 4095], np.random.default_rng(0).integers(0, n, 44)]))
+    got = c[torch.from_numpy(rows).cuda()].double().cpu().numpy()
+    check(got, O.gemm_f64(a[rows], b, alpha), True)
+    # size-independent property: C is linear in alpha (same bits scaled by a power of two)
+    c2 = torch.empty_like(c)
+    G.FP8GEMMScaled(n, n, n, ad.data_ptr(), bd.data_ptr(), c2.data_ptr(), alpha * 4.0, 0, 0, G.OutBF16, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(c2, c * 4.0)
+    # and rows of A map to rows of C: a row permutation of A permutes C
+    perm = torch.randperm(n, device="cuda")
+    c3 = torch.empty_like(c)
+    G.FP8GEMMScaled(n, n, n, ad[perm].contiguous().data_ptr(), bd.data_ptr(), c3.data_ptr(), alpha, 0, 0, G.OutBF16, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(c3, c[perm])
