@@ -13,6 +13,11 @@ struct fa_ctx {
     int device;
     int cc_major, cc_minor;
     bool arch_ok;
+    // Stream-ordered pool the per-call scratch (the fp16 copy of V) is drawn from and
+    // returned to; freed blocks stay cached in the pool, so steady-state calls do not
+    // reach the driver allocator.  Owned by the context, destroyed with it.
+    cudaMemPool_t pool;
+    bool has_pool;
     char last_err[256];
 };
 
@@ -27,7 +32,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // Checks shared by every forward entry.  `who` prefixes messages.
 fa_status_t validate(fa_ctx_t* c, const char* who, const void* q, const void* k, const void* v, const void* o,
                      int bh, int sl, int hd, int causal, int window) {
-    if (!c->arch_ok) { set_err(c, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
+    if (!c->arch_ok || !c->has_pool) { set_err(c, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
     if (!q || !k || !v || !o) { set_err(c, "%s: null pointer in q/k/v/o", who); return FA_ERR_INVALID_ARG; }
     if (bh <= 0 || sl <= 0) { set_err(c, "%s: bh/sl must be > 0", who); return FA_ERR_INVALID_ARG; }
     if (hd != 64 && hd != 128) { set_err(c, "%s: head_dim must be 64 or 128", who); return FA_ERR_UNSUPPORTED_HD; }
@@ -53,8 +58,18 @@ fa_status_t run(fa_ctx_t* c, const char* who, const fa_sm100::LaunchArgs& a) {
         set_err(c, "%s: the calling thread's current device differs from the context's device", who);
         return FA_ERR_INVALID_ARG;
     }
-    e = fa_sm100::launch(a);
+    fa_sm100::LaunchArgs b = a;
+    void* ws = nullptr;
+    e = cudaMallocFromPoolAsync(&ws, fa_sm100::workspace_bytes(a.bh, a.sl, a.hd), c->pool, a.stream);
+    if (e != cudaSuccess) {
+        set_err(c, "%s: workspace allocation: %s", who, cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? FA_ERR_OOM : FA_ERR_CUDA;
+    }
+    b.v16_workspace = ws;
+    e = fa_sm100::launch(b);
+    const cudaError_t fe = cudaFreeAsync(ws, a.stream);  // stream-ordered: released after the kernel
     if (e != cudaSuccess) { set_err(c, "%s: launch: %s", who, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    if (fe != cudaSuccess) { set_err(c, "%s: workspace release: %s", who, cudaGetErrorString(fe)); return FA_ERR_CUDA; }
     return FA_OK;
 }
 
@@ -77,6 +92,23 @@ fa_status_t fa_create(fa_ctx_t** ctx_out) {
         return FA_ERR_CUDA;
     }
     c->arch_ok = (c->cc_major == 10);
+    c->has_pool = false;
+    if (c->arch_ok) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaError_t pe = cudaMemPoolCreate(&c->pool, &props);
+        if (pe != cudaSuccess) {
+            snprintf(c->last_err, sizeof(c->last_err), "fa_create: cudaMemPoolCreate: %s", cudaGetErrorString(pe));
+            *ctx_out = c;
+            return FA_ERR_CUDA;
+        }
+        unsigned long long keep = ~0ull;  // keep freed scratch cached in the pool
+        cudaMemPoolSetAttribute(c->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        c->has_pool = true;
+    }
     *ctx_out = c;  // returned even on an unsupported GPU so the caller can read the reason
     if (!c->arch_ok) {
         snprintf(c->last_err, sizeof(c->last_err),
@@ -87,6 +119,7 @@ fa_status_t fa_create(fa_ctx_t** ctx_out) {
 }
 
 fa_status_t fa_destroy(fa_ctx_t* ctx) {
+    if (ctx && ctx->has_pool) cudaMemPoolDestroy(ctx->pool);  // pending frees complete first (stream-ordered)
     delete ctx;
     return FA_OK;
 }

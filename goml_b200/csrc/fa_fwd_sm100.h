@@ -12,6 +12,7 @@ struct LaunchArgs {
     const void* v;
     void* o;            // [bh, sl, hd] fp16
     float* lse;         // [bh, sl] fp32 natural-log LSE, or nullptr
+    void* v16_workspace = nullptr;  // workspace_bytes(bh, sl, hd) bytes, 128-byte aligned: fp16 copy of V
     int bh, sl, hd;     // hd in {64, 128}
     int causal, window;
     float scale;        // softmax_scale * scale_q * scale_k
@@ -21,6 +22,9 @@ struct LaunchArgs {
     const float* scale_v_dev = nullptr;
     cudaStream_t stream;
 };
+
+// Scratch the forward needs (an fp16 copy of V made by a pre-pass on the same stream).
+size_t workspace_bytes(int bh, int sl, int hd);
 
 // Launches on the calling thread's current device; asynchronous on a.stream.
 cudaError_t launch(const LaunchArgs& a);
