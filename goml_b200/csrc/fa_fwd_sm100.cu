@@ -44,6 +44,20 @@ constexpr int NUM_SOFTMAX_WARPS = 8;
 constexpr int NUM_THREADS = (NUM_SOFTMAX_WARPS + 2) * 32;
 constexpr int MMA_WARP = NUM_SOFTMAX_WARPS;
 constexpr int TMA_WARP = NUM_SOFTMAX_WARPS + 1;
+#ifndef FA_WARP_ARRIVE
+#define FA_WARP_ARRIVE 1
+#endif
+#ifndef FA_MAX_TREE
+#define FA_MAX_TREE 1
+#endif
+constexpr int ARRIVE_SM = FA_WARP_ARRIVE ? NUM_SOFTMAX_WARPS : NUM_SOFTMAX_WARPS * 32;
+constexpr int ARRIVE_X = FA_WARP_ARRIVE ? 2 : 64;
+#ifndef FA_TMA_SLEEP
+#define FA_TMA_SLEEP 0
+#endif
+#ifndef FA_MMA_SLEEP
+#define FA_MMA_SLEEP 0
+#endif
 constexpr float TAU = 6.0f;   // lazy-rescale threshold (log2 units)
 constexpr float POFF = 2.0f;  // P is carried as P * 2^POFF (max 2^(TAU+POFF) = 256, far inside fp16)
 
@@ -55,6 +69,15 @@ enum : uint32_t {
 };
 
 __device__ uint32_t g_fa_status = 0;
+
+#ifdef FA_TRACE
+// Optional in-kernel cycle trace (profiling builds only): one CTA records clock64() at the
+// phase boundaries of softmax warp 0 and of the MMA warp for its first 48 key blocks.
+__device__ long long g_fa_trace[2][48][8];
+#define TRACE(role, j, slot) do { if (trace_on && (j) < 48) g_fa_trace[role][j][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, j, slot) do { } while (0)
+#endif
 
 template <int HD>
 struct Cfg {
@@ -87,6 +110,9 @@ struct Params {
 };
 
 __device__ __forceinline__ float ex2(float x) {
+#ifdef FA_KO_EXP
+    return x * 0.001f;
+#endif
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
@@ -95,6 +121,21 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
+}
+// Packed fp32 pairs (Blackwell fma.rn.f32x2 / add.f32x2): one issue slot for two results.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra, rd;\n\t"
+        "mov.b64 rd, {%0, %1};\n\tmov.b64 ra, {%2, %3};\n\t"
+        "add.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1));
 }
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -142,6 +183,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef FA_TRACE
+    const bool trace_on = (blockIdx.x == 300) && (lane == 0) && (warp == 0 || warp == MMA_WARP);
+#endif
 
     // tile -> (head, query tile); within a head the tiles with the most keys come first
     const int head = blockIdx.x / p.n_qtiles;
@@ -161,11 +205,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             mbar_init(bar_vfull + 8 * s, 1);
             mbar_init(bar_vempty + 8 * s, 1);
             mbar_init(bar_sfull + 8 * s, 1);
-            mbar_init(bar_sempty + 8 * s, NUM_SOFTMAX_WARPS * 32);
-            mbar_init(bar_pfull + 8 * s, NUM_SOFTMAX_WARPS * 32);
+            mbar_init(bar_sempty + 8 * s, ARRIVE_SM);
+            mbar_init(bar_pfull + 8 * s, ARRIVE_SM);
             mbar_init(bar_pvdone + 8 * s, 1);
         }
-        for (int q = 0; q < 4; q++) mbar_init(bar_xchg + 8 * q, 64);
+        for (int q = 0; q < 4; q++) mbar_init(bar_xchg + 8 * q, ARRIVE_X);
         *abort_flag = (sbase & 1023u) ? ST_BAD_SMEM_ALIGN : 0u;
         fence_mbar_init();
     }
@@ -195,10 +239,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 const int s = j & 1;
                 const uint32_t ph = ((j >> 1) & 1) ^ 1;
                 const int key0 = (blk0 + j) * BN;
-                if (!mbar_wait(bar_kempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                if (!mbar_wait<FA_TMA_SLEEP>(bar_kempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+#ifdef FA_KO_TMA
+                if (j >= 2) {  // timing experiment: reuse the tiles loaded for blocks 0 and 1
+                    mbar_arrive(bar_kfull + 8 * s);
+                    if (!mbar_wait<FA_TMA_SLEEP>(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                    mbar_arrive(bar_vfull + 8 * s);
+                    continue;
+                }
+#endif
                 mbar_arrive_expect_tx(bar_kfull + 8 * s, C::K_BYTES);
                 tma_load_3d(sbase + C::OFF_K + s * C::K_BYTES, &tmap_k, bar_kfull + 8 * s, 0, key0, head);
-                if (!mbar_wait(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                if (!mbar_wait<FA_TMA_SLEEP>(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
                 mbar_arrive_expect_tx(bar_vfull + 8 * s, C::V_BYTES);
 #pragma unroll
                 for (int h = 0; h < HD / 64; h++)  // one 64-column (128-byte) slab of d per copy
@@ -222,17 +274,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 mma_commit(bar_kempty + 8 * s);
                 mma_commit(bar_sfull + 8 * s);
             };
-            bool ok = mbar_wait(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
+            bool ok = mbar_wait<FA_MMA_SLEEP>(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
             for (int j = 0; j < 2 && j < nblk && ok; j++) {
-                ok = mbar_wait(bar_kfull + 8 * j, 0, abort_flag, ST_TIMEOUT_MMA);
+                ok = mbar_wait<FA_MMA_SLEEP>(bar_kfull + 8 * j, 0, abort_flag, ST_TIMEOUT_MMA);
                 if (ok) { tc_fence_after(); issue_qk(j); }
             }
             for (int j = 0; j < nblk && ok; j++) {
                 const int s = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
-                ok = mbar_wait(bar_vfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA) &&
-                     mbar_wait(bar_pfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
+                TRACE(1, j, 0);
+                ok = mbar_wait<FA_MMA_SLEEP>(bar_vfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA) &&
+                     mbar_wait<FA_MMA_SLEEP>(bar_pfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
                 if (!ok) break;
+                TRACE(1, j, 1);
                 tc_fence_after();
                 const uint64_t pd = kmajor_desc_sw128(sbase + C::OFF_P + s * C::P_BYTES);
                 const uint32_t vaddr = sbase + C::OFF_V + s * C::V_BYTES;
@@ -243,12 +297,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
                 mma_commit(bar_vempty + 8 * s);
                 mma_commit(bar_pvdone + 8 * s);
+                TRACE(1, j, 2);
                 if (j + 2 < nblk) {
-                    ok = mbar_wait(bar_kfull + 8 * s, ((j + 2) >> 1) & 1, abort_flag, ST_TIMEOUT_MMA) &&
-                         mbar_wait(bar_sempty + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
+                    ok = mbar_wait<FA_MMA_SLEEP>(bar_kfull + 8 * s, ((j + 2) >> 1) & 1, abort_flag, ST_TIMEOUT_MMA) &&
+                         mbar_wait<FA_MMA_SLEEP>(bar_sempty + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
                     if (!ok) break;
+                    TRACE(1, j, 3);
                     tc_fence_after();
                     issue_qk(j + 2);
+                    TRACE(1, j, 4);
                 }
             }
         }
@@ -276,13 +333,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const int b = j & 1;
             const uint32_t ph = (j >> 1) & 1;
             const int key0 = (blk0 + j) * BN;
+            TRACE(0, j, 0);
             if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, ph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+            TRACE(0, j, 1);
             tc_fence_after();
             uint32_t sreg[32];
             tmem_ld_32x32b_x32(tmem_s + lane_off + b * BN + half * 32, sreg);
             tmem_ld_wait();
+            TRACE(0, j, 2);
             tc_fence_before();
-            mbar_arrive(bar_sempty + 8 * b);  // S[b] may be overwritten by the Q K^T two blocks ahead
+            if (FA_WARP_ARRIVE) __syncwarp();
+            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_sempty + 8 * b);  // S[b] may be overwritten by the Q K^T two blocks ahead
 
             if (neg) {
 #pragma unroll
@@ -299,16 +360,33 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     if (key > hi_key || key < lo_key) sreg[c] = 0xff800000u;  // -inf
                 }
             }
+#if FA_MAX_TREE
+            float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one long one
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+#pragma unroll
+                for (int t = 0; t < 4; t++)
+                    mxa[t] = max3(mxa[t], __uint_as_float(sreg[c + 2 * t]), __uint_as_float(sreg[c + 2 * t + 1]));
+            }
+            float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), mxa[3]);
+#else
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(sreg[c]), __uint_as_float(sreg[c + 1]));
+#endif
             // combine with the other half of the row
+#ifndef FA_KO_XCHG
             xchg[(b * 2 + half) * BM + r] = mx;
-            mbar_arrive(bar_xchg + 8 * quad);
+            if (FA_WARP_ARRIVE) __syncwarp();
+            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_xchg + 8 * quad);
             if (!__all_sync(0xffffffffu, mbar_wait(bar_xchg + 8 * quad, xph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
             xph ^= 1;
             mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * BM + r]) * ascale;
+#else
+            mx = fmaxf(mx, 30.f) * ascale;
+#endif
 
+            TRACE(0, j, 3);
             const bool bump = mx > m_ref + TAU;  // true also on the first finite max
             const float m_new = bump ? mx : m_ref;
 
@@ -334,28 +412,42 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 tmem_st_wait();
             }
             m_ref = m_new;
+            TRACE(0, j, 4);
             const float msub = (m_ref == -INFINITY) ? 0.f : m_ref - POFF;
 
-            float l0 = 0.f, l1 = 0.f;
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+            const float nmsub = -msub;
             uint8_t* prow = smem + C::OFF_P + b * C::P_BYTES + r * 128;
 #pragma unroll
             for (int g = 0; g < 4; g++) {  // one 16-byte chunk (8 keys) at a time
                 uint32_t w[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sreg[g * 8 + q * 2 + 0]), ascale, -msub));
-                    const float p1 = ex2(fmaf(__uint_as_float(sreg[g * 8 + q * 2 + 1]), ascale, -msub));
-                    l0 += p0;
-                    l1 += p1;
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(sreg[g * 8 + q * 2 + 0]), __uint_as_float(sreg[g * 8 + q * 2 + 1]),
+                          ascale, ascale, nmsub, nmsub);
+                    const float p0 = ex2(x0);
+                    const float p1 = ex2(x1);
+                    if (q & 1) fadd2(l2, l3, p0, p1); else fadd2(l0, l1, p0, p1);
                     w[q] = pack_half2(p0, p1);
                 }
                 const int chunk = ((half * 4 + g) ^ (r & 7)) * 16;  // 128-byte swizzle: chunk index XOR (row & 7)
+#ifndef FA_KO_PSTORE
                 *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(w[0], w[1], w[2], w[3]);
+#else
+                if (w[0] == 0x12345678u && w[1] == w[2] && w[3] == 77u) *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(w[0], w[1], w[2], w[3]);
+#endif
             }
+            l0 += l2;
+            l1 += l3;
             l += l0 + l1;
-            fence_proxy_async_smem();
+            TRACE(0, j, 5);
+            fence_proxy_async_smem();  // every writer publishes its own stores to the async proxy
+            TRACE(0, j, 6);
             tc_fence_before();
-            mbar_arrive(bar_pfull + 8 * b);
+            if (FA_WARP_ARRIVE) __syncwarp();
+            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_pfull + 8 * b);
+            TRACE(0, j, 7);
         }
 
         // epilogue: O / l (times the V dequantisation scale) -> fp16
@@ -366,7 +458,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             // (slot 0/1 of the exchange area was last read two or more rendezvous ago, or is read below
             //  only after the rendezvous that follows this write)
             xchg[((nblk & 1) * 2 + half) * BM + r] = l;
-            mbar_arrive(bar_xchg + 8 * quad);
+            if (FA_WARP_ARRIVE) __syncwarp();
+            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_xchg + 8 * quad);
             const bool met = __all_sync(0xffffffffu, mbar_wait(bar_xchg + 8 * quad, xph, abort_flag, ST_TIMEOUT_SOFTMAX));
             if (met) l += xchg[((nblk & 1) * 2 + (half ^ 1)) * BM + r];
             const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
@@ -472,6 +565,13 @@ cudaError_t launch(const LaunchArgs& a) {
     }
     return a.hd == 128 ? launch_hd<128>(a, g_dev[dev].num_sms) : launch_hd<64>(a, g_dev[dev].num_sms);
 }
+
+#ifdef FA_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_trace_read(long long* out) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * 2 * 48 * 8);
+}
+#endif
 
 int device_status() {
     cudaError_t e = cudaDeviceSynchronize();
