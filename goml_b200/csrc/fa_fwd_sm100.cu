@@ -9,20 +9,25 @@
 //                    every e4m3 value is an fp16 value; HBM-bound, <2% of the time)
 //   TMA            : swizzled tiles, 3-D maps over [BH,S,D] so a tile never crosses a head
 //   S = Q K^T      : tcgen05.mma kind::f8f6f4 on the e4m3 codes, 128x64 fp32
-//                    accumulator in TMEM, double buffered
-//   softmax        : 8 warps, two threads per query row (32 keys each), fp32 running
-//                    max/sum in the log2 domain, scale folded into one FFMA per score,
-//                    lazy O rescale (only when the max grows by more than 2^TAU)
-//   P              : kept in fp16 (11-bit significand) in swizzled shared memory.
-//                    The reference rounds P to e4m3 (3-bit mantissa); for zero-mean V
-//                    that rounding alone costs ~2.5e-2 mean relative error, above the
-//                    1e-2 bar, so P V runs as an fp16 MMA instead
-//   O += P V       : tcgen05.mma kind::f16 with V consumed MN-major straight from the
-//                    TMA tile (no shared-memory transpose), fp32 accumulator in TMEM
+//                    accumulator in TMEM, double buffered so the next block's scores are
+//                    ready before the softmax of the current one ends
+//   softmax        : 4 warps, one query row per thread (tcgen05.ld 32x32b), fp32 running
+//                    max/sum in the log2 domain, scale folded into one packed FFMA per two
+//                    scores, lazy O rescale (only when the max grows by more than 2^TAU)
+//   P              : kept in fp16 (11-bit significand) and written back to TENSOR MEMORY
+//                    over the first half of its S buffer.  The reference rounds P to e4m3 (3-bit
+//                    mantissa); for zero-mean V that rounding alone costs ~2.5e-2 mean
+//                    relative error, above the 1e-2 bar, so P V runs as an fp16 MMA
+//   O += P V       : tcgen05.mma kind::f16, A = P read from TMEM, B = V consumed MN-major
+//                    straight from the TMA tile (no shared-memory transpose), fp32
+//                    accumulator in TMEM
 //   epilogue       : O * (v_descale / l) -> fp16, 128-bit stores; LSE.
 //
-// One CTA = one 128-row query tile of one head; 10 warps (8 softmax, 1 MMA issuer,
-// 1 TMA producer); two CTAs share an SM.  Every mbarrier wait is bounded.
+// The tensor core reads shared-memory operands at 128 B/clk/SM, which is what bounds both
+// MMAs here; keeping P out of shared memory keeps that traffic near the exponential-unit
+// time, which is the next bound (16 ex2 per clock per SM).  One CTA = one 128-row query tile of one head; 6 warps (4 softmax,
+// 1 MMA issuer, 1 TMA producer); two CTAs share an SM so one CTA's softmax overlaps the
+// other's MMAs.  Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -40,24 +45,11 @@ namespace {
 
 constexpr int BM = 128;  // query rows per CTA (= TMEM lanes)
 constexpr int BN = 64;   // keys per block
-constexpr int NUM_SOFTMAX_WARPS = 8;
+constexpr int STAGES = 3; // K / V shared-memory ring depth
+constexpr int NUM_SOFTMAX_WARPS = 4;   // one thread per query row
 constexpr int NUM_THREADS = (NUM_SOFTMAX_WARPS + 2) * 32;
 constexpr int MMA_WARP = NUM_SOFTMAX_WARPS;
 constexpr int TMA_WARP = NUM_SOFTMAX_WARPS + 1;
-#ifndef FA_WARP_ARRIVE
-#define FA_WARP_ARRIVE 1
-#endif
-#ifndef FA_MAX_TREE
-#define FA_MAX_TREE 1
-#endif
-constexpr int ARRIVE_SM = FA_WARP_ARRIVE ? NUM_SOFTMAX_WARPS : NUM_SOFTMAX_WARPS * 32;
-constexpr int ARRIVE_X = FA_WARP_ARRIVE ? 2 : 64;
-#ifndef FA_TMA_SLEEP
-#define FA_TMA_SLEEP 0
-#endif
-#ifndef FA_MMA_SLEEP
-#define FA_MMA_SLEEP 0
-#endif
 constexpr float TAU = 6.0f;   // lazy-rescale threshold (log2 units)
 constexpr float POFF = 2.0f;  // P is carried as P * 2^POFF (max 2^(TAU+POFF) = 256, far inside fp16)
 
@@ -79,21 +71,23 @@ __device__ long long g_fa_trace[2][48][8];
 #define TRACE(role, j, slot) do { } while (0)
 #endif
 
+// Shared memory holds only TMA-written operand tiles.  Both MMAs are limited by how fast the
+// tensor core can read its shared-memory operands (128 B/clk/SM), so P never goes through
+// shared memory: it is written to tensor memory and read from there as the A operand.
 template <int HD>
 struct Cfg {
     static constexpr int Q_BYTES = BM * HD;
     static constexpr int K_BYTES = BN * HD;
     static constexpr int V_BYTES = BN * HD * 2;       // fp16
     static constexpr int V_HALF_BYTES = BN * 128;     // one 64-wide (128-byte) slab of d
-    static constexpr int P_BYTES = BM * BN * 2;       // fp16, 128-byte rows
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
-    static constexpr int OFF_V = OFF_K + 2 * K_BYTES;
-    static constexpr int OFF_P = OFF_V + 2 * V_BYTES;
-    static constexpr int OFF_X = OFF_P + 2 * P_BYTES;  // row-max / row-sum exchange between the two halves of a row
-    static constexpr int OFF_BAR = OFF_X + 2 * 2 * BM * 4;
+    static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
+    static constexpr int OFF_BAR = OFF_V + STAGES * V_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
-    static constexpr int TMEM_COLS = 256;  // S: 2 x 64 columns at [0,128)   O: [128, 128+HD)
+    // TMEM: S[0], S[1] (64 fp32 columns each; P of the same block, 32 columns of packed fp16
+    //       pairs, overwrites the first half of its S buffer)   O at [128, 128 + HD)
+    static constexpr int TMEM_COLS = 256;
     static constexpr int O_COL = 128;
 };
 
@@ -110,9 +104,6 @@ struct Params {
 };
 
 __device__ __forceinline__ float ex2(float x) {
-#ifdef FA_KO_EXP
-    return x * 0.001f;
-#endif
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
@@ -168,18 +159,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + C::OFF_BAR;
     const uint32_t bar_q = bars;
-    const uint32_t bar_kfull = bars + 8;      // [2]
-    const uint32_t bar_kempty = bars + 24;    // [2]
-    const uint32_t bar_vfull = bars + 40;     // [2]
-    const uint32_t bar_vempty = bars + 56;    // [2]
-    const uint32_t bar_sfull = bars + 72;     // [2]
-    const uint32_t bar_sempty = bars + 88;    // [2]
-    const uint32_t bar_pfull = bars + 104;    // [2]
-    const uint32_t bar_pvdone = bars + 120;   // [2]
-    const uint32_t bar_xchg = bars + 160;     // [4] one per lane quadrant: the two half-row warps meet here
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 144);
+    const uint32_t bar_kfull = bars + 8;                  // [STAGES]
+    const uint32_t bar_kempty = bar_kfull + 8 * STAGES;   // [STAGES]
+    const uint32_t bar_vfull = bar_kempty + 8 * STAGES;   // [STAGES]
+    const uint32_t bar_vempty = bar_vfull + 8 * STAGES;   // [STAGES]
+    const uint32_t bar_sfull = bar_vempty + 8 * STAGES;   // [2] S[b] = Q K^T complete (and every earlier MMA)
+    const uint32_t bar_pfull = bar_sfull + 16;            // [2] softmax wrote P into S[b] (and rescaled O if needed)
+    const uint32_t bar_pvdone = bar_pfull + 16;           // [2] O += P V of a block using S[b] complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 240);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    volatile float* xchg = reinterpret_cast<volatile float*>(smem + C::OFF_X);  // [slot 2][half 2][row 128]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -199,17 +187,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_kfull + 8 * s, 1);
             mbar_init(bar_kempty + 8 * s, 1);
             mbar_init(bar_vfull + 8 * s, 1);
             mbar_init(bar_vempty + 8 * s, 1);
-            mbar_init(bar_sfull + 8 * s, 1);
-            mbar_init(bar_sempty + 8 * s, ARRIVE_SM);
-            mbar_init(bar_pfull + 8 * s, ARRIVE_SM);
-            mbar_init(bar_pvdone + 8 * s, 1);
         }
-        for (int q = 0; q < 4; q++) mbar_init(bar_xchg + 8 * q, ARRIVE_X);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar_sfull + 8 * b, 1);
+            mbar_init(bar_pfull + 8 * b, NUM_SOFTMAX_WARPS * 32);
+            mbar_init(bar_pvdone + 8 * b, 1);
+        }
         *abort_flag = (sbase & 1023u) ? ST_BAD_SMEM_ALIGN : 0u;
         fence_mbar_init();
     }
@@ -235,75 +223,68 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             prefetch_tmap(&tmap_v);
             mbar_arrive_expect_tx(bar_q, C::Q_BYTES);
             tma_load_3d(sbase + C::OFF_Q, &tmap_q, bar_q, 0, q0, head);
+            int s = 0;
+            uint32_t ph = 1;  // "previous phase complete": the rings start empty
             for (int j = 0; j < nblk; j++) {
-                const int s = j & 1;
-                const uint32_t ph = ((j >> 1) & 1) ^ 1;
                 const int key0 = (blk0 + j) * BN;
-                if (!mbar_wait<FA_TMA_SLEEP>(bar_kempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
-#ifdef FA_KO_TMA
-                if (j >= 2) {  // timing experiment: reuse the tiles loaded for blocks 0 and 1
-                    mbar_arrive(bar_kfull + 8 * s);
-                    if (!mbar_wait<FA_TMA_SLEEP>(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
-                    mbar_arrive(bar_vfull + 8 * s);
-                    continue;
-                }
-#endif
+                if (!mbar_wait(bar_kempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
                 mbar_arrive_expect_tx(bar_kfull + 8 * s, C::K_BYTES);
                 tma_load_3d(sbase + C::OFF_K + s * C::K_BYTES, &tmap_k, bar_kfull + 8 * s, 0, key0, head);
-                if (!mbar_wait<FA_TMA_SLEEP>(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                if (!mbar_wait(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
                 mbar_arrive_expect_tx(bar_vfull + 8 * s, C::V_BYTES);
 #pragma unroll
                 for (int h = 0; h < HD / 64; h++)  // one 64-column (128-byte) slab of d per copy
                     tma_load_3d(sbase + C::OFF_V + s * C::V_BYTES + h * C::V_HALF_BYTES, &tmap_v, bar_vfull + 8 * s,
                                 h * 64, key0, head);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == MMA_WARP) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc_e4m3_f32(BM, BN, 0, 0);
-            constexpr uint32_t idesc_pv = make_idesc_f16_f32(BM, HD, 0, 1);  // V is MN-major
+            constexpr uint32_t idesc_pv = make_idesc_f16_f32(BM, HD, 0, 1);  // A = P from TMEM, V is MN-major
             auto qk_desc = [&](uint32_t addr) { return HD == 128 ? kmajor_desc_sw128(addr) : kmajor_desc_sw64(addr); };
-            auto issue_qk = [&](int j) {
-                const int s = j & 1;
+            // K ring position of the next Q K^T, V ring position of the next P V
+            int ks = 0, vs = 0;
+            uint32_t kph = 0, vph = 0;
+            bool ok = true;
+            auto issue_qk = [&](int j) {  // S[j & 1] = Q K(j)^T
+                ok = mbar_wait(bar_kfull + 8 * ks, kph, abort_flag, ST_TIMEOUT_MMA);
+                if (!ok) return;
+                tc_fence_after();
                 const uint64_t qd = qk_desc(sbase + C::OFF_Q);
-                const uint64_t kd = qk_desc(sbase + C::OFF_K + s * C::K_BYTES);
+                const uint64_t kd = qk_desc(sbase + C::OFF_K + ks * C::K_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 32; k++)
-                    mma_f8f6f4_ss(tmem_s + s * BN, qd + 2 * k, kd + 2 * k, idesc_qk, k != 0);
-                mma_commit(bar_kempty + 8 * s);
-                mma_commit(bar_sfull + 8 * s);
+                    mma_f8f6f4_ss(tmem_s + (j & 1) * BN, qd + 2 * k, kd + 2 * k, idesc_qk, k != 0);
+                mma_commit(bar_kempty + 8 * ks);
+                mma_commit(bar_sfull + 8 * (j & 1));
+                if (++ks == STAGES) { ks = 0; kph ^= 1; }
             };
-            bool ok = mbar_wait<FA_MMA_SLEEP>(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
-            for (int j = 0; j < 2 && j < nblk && ok; j++) {
-                ok = mbar_wait<FA_MMA_SLEEP>(bar_kfull + 8 * j, 0, abort_flag, ST_TIMEOUT_MMA);
-                if (ok) { tc_fence_after(); issue_qk(j); }
-            }
+            ok = mbar_wait(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
+            for (int j = 0; j < 2 && j < nblk && ok; j++) issue_qk(j);
             for (int j = 0; j < nblk && ok; j++) {
-                const int s = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
+                const int b = j & 1;
                 TRACE(1, j, 0);
-                ok = mbar_wait<FA_MMA_SLEEP>(bar_vfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA) &&
-                     mbar_wait<FA_MMA_SLEEP>(bar_pfull + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
+                ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, ST_TIMEOUT_MMA) &&
+                     mbar_wait(bar_pfull + 8 * b, (j >> 1) & 1, abort_flag, ST_TIMEOUT_MMA);
                 if (!ok) break;
                 TRACE(1, j, 1);
                 tc_fence_after();
-                const uint64_t pd = kmajor_desc_sw128(sbase + C::OFF_P + s * C::P_BYTES);
-                const uint32_t vaddr = sbase + C::OFF_V + s * C::V_BYTES;
+                const uint32_t vaddr = sbase + C::OFF_V + vs * C::V_BYTES;
 #pragma unroll
-                for (int k = 0; k < BN / 16; k++) {  // 16 keys per MMA: P advances 32 bytes, V 16 rows of 128 bytes
+                for (int k = 0; k < BN / 16; k++) {  // 16 keys per MMA: 8 TMEM columns of P, 16 rows of V
                     const uint64_t vd = mnmajor_desc_sw128(vaddr + k * 16 * 128, C::V_HALF_BYTES);
-                    mma_f16_ss(tmem_o, pd + 2 * k, vd, idesc_pv, (j | k) != 0);
+                    mma_f16_ts(tmem_o, tmem_s + b * BN + 8 * k, vd, idesc_pv, (j | k) != 0);
                 }
-                mma_commit(bar_vempty + 8 * s);
-                mma_commit(bar_pvdone + 8 * s);
+                mma_commit(bar_vempty + 8 * vs);
+                mma_commit(bar_pvdone + 8 * b);
+                if (++vs == STAGES) { vs = 0; vph ^= 1; }
                 TRACE(1, j, 2);
+                // S[b] is rewritten by the Q K^T two blocks ahead; it is issued behind this P V on the
+                // same in-order tensor pipe, so P(j) has been read before S(j+2) lands on it
                 if (j + 2 < nblk) {
-                    ok = mbar_wait<FA_MMA_SLEEP>(bar_kfull + 8 * s, ((j + 2) >> 1) & 1, abort_flag, ST_TIMEOUT_MMA) &&
-                         mbar_wait<FA_MMA_SLEEP>(bar_sempty + 8 * s, ph, abort_flag, ST_TIMEOUT_MMA);
-                    if (!ok) break;
-                    TRACE(1, j, 3);
-                    tc_fence_after();
                     issue_qk(j + 2);
                     TRACE(1, j, 4);
                 }
@@ -311,11 +292,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
     } else {
         // ------------------------------------------- softmax / correction / epilogue
-        const int quad = warp & 3;               // TMEM lane quadrant of this warp
-        const int half = warp >> 2;              // which 32 of the block's 64 keys this thread owns
-        const int r = quad * 32 + lane;          // row of the tile = TMEM lane
+        const int r = threadIdx.x;               // row of the tile = TMEM lane (one thread per row)
         const int qi = q0 + r;                   // query index in the sequence
-        const uint32_t lane_off = uint32_t(quad * 32) << 16;
+        const uint32_t lane_off = uint32_t(warp * 32) << 16;
         float scale_log2 = p.scale_log2;
         if (p.sq) scale_log2 *= __ldg(p.sq);
         if (p.sk) scale_log2 *= __ldg(p.sk);
@@ -323,76 +302,52 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         float ascale = fabsf(scale_log2);
         if (ascale == 0.f) ascale = 1e-30f;      // keeps -inf * scale = -inf for masked keys
         float m_ref = -INFINITY;                 // reference max used in the exponent (log2 units)
-        float l = 0.f;                           // this thread's partial sum of P * 2^POFF
+        float l = 0.f;                           // running sum of P * 2^POFF
         bool ok = true;
-        uint32_t xph = 0;                        // phase of the half-row rendezvous barrier
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
 
         for (int j = 0; j < nblk; j++) {
-            const int b = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
             const int key0 = (blk0 + j) * BN;
             TRACE(0, j, 0);
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, ph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+            const int b = j & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, (j >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
             TRACE(0, j, 1);
             tc_fence_after();
-            uint32_t sreg[32];
-            tmem_ld_32x32b_x32(tmem_s + lane_off + b * BN + half * 32, sreg);
+            uint32_t sreg[BN];
+#pragma unroll
+            for (int c = 0; c < BN / 32; c++) tmem_ld_32x32b_x32(tmem_s + lane_off + b * BN + c * 32, sreg + c * 32);
             tmem_ld_wait();
             TRACE(0, j, 2);
-            tc_fence_before();
-            if (FA_WARP_ARRIVE) __syncwarp();
-            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_sempty + 8 * b);  // S[b] may be overwritten by the Q K^T two blocks ahead
 
             if (neg) {
 #pragma unroll
-                for (int c = 0; c < 32; c++) sreg[c] ^= 0x80000000u;
+                for (int c = 0; c < BN; c++) sreg[c] ^= 0x80000000u;
             }
             // does this block need per-element masking?  (uniform across the CTA)
             const bool mask_blk = (key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
                                   (p.window > 0 && key0 < q0 + BM - p.window);
             if (mask_blk) {
-                const int kbase = key0 + half * 32;
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    const int key = kbase + c;
+                for (int c = 0; c < BN; c++) {
+                    const int key = key0 + c;
                     if (key > hi_key || key < lo_key) sreg[c] = 0xff800000u;  // -inf
                 }
             }
-#if FA_MAX_TREE
-            float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one long one
+            float mxa[8];  // eight short dependency chains
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
+            for (int t = 0; t < 8; t++) mxa[t] = fmaxf(__uint_as_float(sreg[2 * t]), __uint_as_float(sreg[2 * t + 1]));
 #pragma unroll
-                for (int t = 0; t < 4; t++)
+            for (int c = 16; c < BN; c += 16) {
+#pragma unroll
+                for (int t = 0; t < 8; t++)
                     mxa[t] = max3(mxa[t], __uint_as_float(sreg[c + 2 * t]), __uint_as_float(sreg[c + 2 * t + 1]));
             }
-            float mx = fmaxf(max3(mxa[0], mxa[1], mxa[2]), mxa[3]);
-#else
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(sreg[c]), __uint_as_float(sreg[c + 1]));
-#endif
-            // combine with the other half of the row
-#ifndef FA_KO_XCHG
-            xchg[(b * 2 + half) * BM + r] = mx;
-            if (FA_WARP_ARRIVE) __syncwarp();
-            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_xchg + 8 * quad);
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_xchg + 8 * quad, xph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
-            xph ^= 1;
-            mx = fmaxf(mx, xchg[(b * 2 + (half ^ 1)) * BM + r]) * ascale;
-#else
-            mx = fmaxf(mx, 30.f) * ascale;
-#endif
-
+            const float mx = fmaxf(max3(max3(mxa[0], mxa[1], mxa[2]), max3(mxa[3], mxa[4], mxa[5]), mxa[6]), mxa[7]) * ascale;
             TRACE(0, j, 3);
+
             const bool bump = mx > m_ref + TAU;  // true also on the first finite max
             const float m_new = bump ? mx : m_ref;
-
-            if (j >= 2) {  // P[b] is free once the P V two blocks back has finished
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * b, ((j - 2) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
-            }
             if (j > 0 && __any_sync(0xffffffffu, bump)) {
                 // O is final only once the previous P V has finished
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
@@ -400,75 +355,54 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
                 l *= f;
 #pragma unroll
-                for (int c = 0; c < HD / 32; c++) {  // this thread rescales its half of the row's O columns
+                for (int c = 0; c < HD / 16; c++) {
                     uint32_t o[16];
-                    const uint32_t addr = tmem_o + lane_off + half * (HD / 2) + c * 16;
-                    tmem_ld_32x32b_x16(addr, o);
+                    tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tmem_st_32x32b_x16(addr, o);
+                    tmem_st_32x32b_x16(tmem_o + lane_off + c * 16, o);
                 }
-                tmem_st_wait();
             }
             m_ref = m_new;
             TRACE(0, j, 4);
-            const float msub = (m_ref == -INFINITY) ? 0.f : m_ref - POFF;
+            const float nmsub = (m_ref == -INFINITY) ? 0.f : POFF - m_ref;
 
             float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-            const float nmsub = -msub;
-            uint8_t* prow = smem + C::OFF_P + b * C::P_BYTES + r * 128;
 #pragma unroll
-            for (int g = 0; g < 4; g++) {  // one 16-byte chunk (8 keys) at a time
-                uint32_t w[4];
+            for (int g = 0; g < BN / 32; g++) {  // 32 keys -> 16 TMEM columns of packed fp16 pairs
+                uint32_t w[16];
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
+                for (int q = 0; q < 16; q++) {
                     float x0, x1;
-                    ffma2(x0, x1, __uint_as_float(sreg[g * 8 + q * 2 + 0]), __uint_as_float(sreg[g * 8 + q * 2 + 1]),
+                    ffma2(x0, x1, __uint_as_float(sreg[g * 32 + q * 2 + 0]), __uint_as_float(sreg[g * 32 + q * 2 + 1]),
                           ascale, ascale, nmsub, nmsub);
                     const float p0 = ex2(x0);
                     const float p1 = ex2(x1);
                     if (q & 1) fadd2(l2, l3, p0, p1); else fadd2(l0, l1, p0, p1);
                     w[q] = pack_half2(p0, p1);
                 }
-                const int chunk = ((half * 4 + g) ^ (r & 7)) * 16;  // 128-byte swizzle: chunk index XOR (row & 7)
-#ifndef FA_KO_PSTORE
-                *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(w[0], w[1], w[2], w[3]);
-#else
-                if (w[0] == 0x12345678u && w[1] == w[2] && w[3] == 77u) *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(w[0], w[1], w[2], w[3]);
-#endif
+                tmem_st_32x32b_x16(tmem_s + lane_off + b * BN + g * 16, w);  // P overwrites the first half of S[b]
             }
-            l0 += l2;
-            l1 += l3;
-            l += l0 + l1;
+            l += (l0 + l1) + (l2 + l3);
             TRACE(0, j, 5);
-            fence_proxy_async_smem();  // every writer publishes its own stores to the async proxy
+            tmem_st_wait();
             TRACE(0, j, 6);
             tc_fence_before();
-            if (FA_WARP_ARRIVE) __syncwarp();
-            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_pfull + 8 * b);
+            mbar_arrive(bar_pfull + 8 * b);
             TRACE(0, j, 7);
         }
 
         // epilogue: O / l (times the V dequantisation scale) -> fp16
-        const int last = nblk - 1;
-        if (ok && __all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * (last & 1), (last >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) {
+        if (ok && __all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * ((nblk - 1) & 1), ((nblk - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) {
             tc_fence_after();
-            // full row sum = the two halves' partial sums
-            // (slot 0/1 of the exchange area was last read two or more rendezvous ago, or is read below
-            //  only after the rendezvous that follows this write)
-            xchg[((nblk & 1) * 2 + half) * BM + r] = l;
-            if (FA_WARP_ARRIVE) __syncwarp();
-            if (!FA_WARP_ARRIVE || lane == 0) mbar_arrive(bar_xchg + 8 * quad);
-            const bool met = __all_sync(0xffffffffu, mbar_wait(bar_xchg + 8 * quad, xph, abort_flag, ST_TIMEOUT_SOFTMAX));
-            if (met) l += xchg[((nblk & 1) * 2 + (half ^ 1)) * BM + r];
             const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
             const float inv = (l > 0.f) ? vds / l : 0.f;
-            __half* orow = p.o + ((size_t)head * p.sl + qi) * HD + half * (HD / 2);
+            __half* orow = p.o + ((size_t)head * p.sl + qi) * HD;
 #pragma unroll
-            for (int c = 0; c < HD / 32; c++) {
+            for (int c = 0; c < HD / 16; c++) {
                 uint32_t o[16];
-                tmem_ld_32x32b_x16(tmem_o + lane_off + half * (HD / 2) + c * 16, o);
+                tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
                 tmem_ld_wait();
                 if (qi < p.sl) {
 #pragma unroll
@@ -482,7 +416,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     }
                 }
             }
-            if (p.lse && half == 0 && qi < p.sl) {
+            if (p.lse && qi < p.sl) {
                 // sum_j exp(s_j) = l * 2^(m_ref - POFF)  ->  natural-log LSE
                 p.lse[(size_t)head * p.sl + qi] =
                     (l > 0.f) ? (m_ref - POFF + log2f(l)) * 0.6931471805599453f : -INFINITY;
