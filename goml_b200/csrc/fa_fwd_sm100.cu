@@ -334,34 +334,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     if (key > hi_key || key < lo_key) sreg[c] = 0xff800000u;  // -inf
                 }
             }
-            // exponentials of the whole block against reference max m: P -> TMEM, returns the row's block sum
-            auto exp_block = [&](float m) -> float {
-                const float nmsub = (m == -INFINITY) ? 0.f : POFF - m;
-                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-                for (int g = 0; g < BN / 32; g++) {  // 32 keys -> 16 TMEM columns of packed fp16 pairs
-                    uint32_t w[16];
-#pragma unroll
-                    for (int q = 0; q < 16; q++) {
-                        float x0, x1;
-                        ffma2(x0, x1, __uint_as_float(sreg[g * 32 + q * 2 + 0]), __uint_as_float(sreg[g * 32 + q * 2 + 1]),
-                              ascale, ascale, nmsub, nmsub);
-                        const float p0 = ex2(x0);
-                        const float p1 = ex2(x1);
-                        if (q & 1) fadd2(l2, l3, p0, p1); else fadd2(l0, l1, p0, p1);
-                        w[q] = pack_half2(p0, p1);
-                    }
-                    tmem_st_32x32b_x16(tmem_s + lane_off + b * BN + g * 16, w);  // P overwrites the first half of S[b]
-                }
-                return (l0 + l1) + (l2 + l3);
-            };
-            // Speculation: from the second block on, the exponentials are started against the reference
-            // max carried over from earlier blocks, so they do not wait for this block's row max — the
-            // max pass below is independent work the scheduler interleaves with them.  Only if some row
-            // of the warp grew past the lazy-rescale threshold is the block redone with the new reference.
-            float lblk = 0.f;
-            if (j > 0) lblk = exp_block(m_ref);
-
             float mxa[8];  // eight short dependency chains
 #pragma unroll
             for (int t = 0; t < 8; t++) mxa[t] = fmaxf(__uint_as_float(sreg[2 * t]), __uint_as_float(sreg[2 * t + 1]));
@@ -375,29 +347,44 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             TRACE(0, j, 3);
 
             const bool bump = mx > m_ref + TAU;  // true also on the first finite max
-            if (j == 0 || __any_sync(0xffffffffu, bump)) {
-                const float m_new = bump ? mx : m_ref;
-                if (j > 0) {
-                    // O is final only once the previous P V has finished
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
-                    tc_fence_after();
-                    const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
-                    l *= f;
+            const float m_new = bump ? mx : m_ref;
+            if (j > 0 && __any_sync(0xffffffffu, bump)) {
+                // O is final only once the previous P V has finished
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+                tc_fence_after();
+                const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
+                l *= f;
 #pragma unroll
-                    for (int c = 0; c < HD / 16; c++) {
-                        uint32_t o[16];
-                        tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
-                        tmem_ld_wait();
+                for (int c = 0; c < HD / 16; c++) {
+                    uint32_t o[16];
+                    tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                        tmem_st_32x32b_x16(tmem_o + lane_off + c * 16, o);
-                    }
+                    for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                    tmem_st_32x32b_x16(tmem_o + lane_off + c * 16, o);
                 }
-                m_ref = m_new;
-                lblk = exp_block(m_ref);  // (re)do the block against the new reference
             }
-            l += lblk;
+            m_ref = m_new;
             TRACE(0, j, 4);
+            const float nmsub = (m_ref == -INFINITY) ? 0.f : POFF - m_ref;
+
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+            for (int g = 0; g < BN / 32; g++) {  // 32 keys -> 16 TMEM columns of packed fp16 pairs
+                uint32_t w[16];
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(sreg[g * 32 + q * 2 + 0]), __uint_as_float(sreg[g * 32 + q * 2 + 1]),
+                          ascale, ascale, nmsub, nmsub);
+                    const float p0 = ex2(x0);
+                    const float p1 = ex2(x1);
+                    if (q & 1) fadd2(l2, l3, p0, p1); else fadd2(l0, l1, p0, p1);
+                    w[q] = pack_half2(p0, p1);
+                }
+                tmem_st_32x32b_x16(tmem_s + lane_off + b * BN + g * 16, w);  // P overwrites the first half of S[b]
+            }
+            l += (l0 + l1) + (l2 + l3);
             TRACE(0, j, 5);
             tmem_st_wait();
             TRACE(0, j, 6);
