@@ -33,6 +33,9 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <stdio.h>
+
+#include "../../include/fa_sm120.h"
 #include "fa_fwd_sm100.h"
 #include "sm100_ptx.cuh"
 #include "tmap.cuh"
@@ -517,4 +520,90 @@ int device_status() {
     return (int)code;
 }
 
+// ----------------------------------------------------------------------------------------
+// Forward pass for callers that must not allocate.
+//
+// The regular entry points borrow their scratch (the fp16 copy of V) from a memory pool.
+// Some callers cannot do that: code embedded in a framework that reserved the whole GPU up
+// front and forbids any later cudaMalloc-family call, and real-time or safety-certified
+// processes whose device memory map is frozen after start-up.  For them the scratch lives in
+// the fixed device array below, which every GPU that loads this library carries until the
+// process exits (32 MiB).  That caps one call at FA_NOALLOC_MAX_ELEMS elements of V.
+//
+// The array is shared by every call on that GPU and keeps the previous call's contents.
+// Nothing in it has to start at zero: the pre-pass rewrites every element the kernel will read
+// before the kernel runs.  Two calls whose GPU work overlaps (different streams) race on it;
+// issue them on one stream or serialise them.  The first call on each device also looks up the
+// array's device address and sets kernel attributes; make that first call before starting any
+// stream capture.
+// ----------------------------------------------------------------------------------------
+constexpr size_t FA_NOALLOC_MAX_ELEMS = (size_t)16 << 20;  // batch_heads * seq_len * head_dim <= 16 Mi
+static __device__ __align__(256) uint16_t g_noalloc_v16[FA_NOALLOC_MAX_ELEMS];
+
+namespace {
+// In host code `g_noalloc_v16` is only a stand-in for the device array; the device address is
+// looked up once per device (with that device current) and cached.
+void* g_noalloc_ptr[64];
+bool g_noalloc_ready[64];
+
+void write_msg(char* err, int err_len, const char* msg) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", msg);
+}
+}  // namespace
+
 }  // namespace fa_sm100
+
+extern "C" __attribute__((visibility("default")))
+fa_status_t fa_forward_noalloc(const fa_forward_args_t* g, char* err, int err_len) {
+    using namespace fa_sm100;
+    if (err && err_len > 0) err[0] = '\0';
+    if (!g) { write_msg(err, err_len, "fa_forward_noalloc: null argument block"); return FA_ERR_INVALID_ARG; }
+    if (!g->q || !g->k || !g->v || !g->o) { write_msg(err, err_len, "fa_forward_noalloc: null pointer in q/k/v/o"); return FA_ERR_INVALID_ARG; }
+    if (g->batch_heads <= 0 || g->seq_len <= 0) { write_msg(err, err_len, "fa_forward_noalloc: bh/sl must be > 0"); return FA_ERR_INVALID_ARG; }
+    if (g->head_dim != 64 && g->head_dim != 128) { write_msg(err, err_len, "fa_forward_noalloc: head_dim must be 64 or 128"); return FA_ERR_UNSUPPORTED_HD; }
+    if (g->window < 0 || g->window > g->seq_len) { write_msg(err, err_len, "fa_forward_noalloc: window must be in [0, seq_len]"); return FA_ERR_INVALID_ARG; }
+    if (g->causal != 0 && g->causal != 1) { write_msg(err, err_len, "fa_forward_noalloc: causal must be 0 or 1"); return FA_ERR_INVALID_ARG; }
+    const uintptr_t align_or = reinterpret_cast<uintptr_t>(g->q) | reinterpret_cast<uintptr_t>(g->k) |
+                               reinterpret_cast<uintptr_t>(g->v) | reinterpret_cast<uintptr_t>(g->o);
+    if (align_or & 15) { write_msg(err, err_len, "fa_forward_noalloc: q/k/v/o must be 16-byte aligned"); return FA_ERR_INVALID_ARG; }
+    const size_t elems = (size_t)g->batch_heads * (size_t)g->seq_len * (size_t)g->head_dim;
+    if (elems > FA_NOALLOC_MAX_ELEMS) {
+        if (err && err_len > 0)
+            snprintf(err, (size_t)err_len,
+                     "fa_forward_noalloc: batch_heads*seq_len*head_dim = %zu exceeds the fixed scratch of %zu elements "
+                     "(32 MiB); split the batch or use fa_forward_ex", elems, FA_NOALLOC_MAX_ELEMS);
+        return FA_ERR_UNSUPPORTED_SHAPE;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) { write_msg(err, err_len, "fa_forward_noalloc: cudaGetDevice failed"); return FA_ERR_CUDA; }
+    if (!g_noalloc_ready[dev]) {
+        // one-time set-up for this device (do it before any stream capture): architecture check and
+        // the device address of the scratch array
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) { write_msg(err, err_len, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+        if (major != 10) { write_msg(err, err_len, "fa_forward_noalloc: GPU is not compute capability 10.x"); return FA_ERR_UNSUPPORTED_ARCH; }
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_v16);
+        if (e != cudaSuccess || !ptr) {
+            if (err && err_len > 0) snprintf(err, (size_t)err_len, "fa_forward_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return FA_ERR_CUDA;
+        }
+        g_noalloc_ptr[dev] = ptr;
+        g_noalloc_ready[dev] = true;
+    }
+    LaunchArgs a{};
+    a.q = g->q; a.k = g->k; a.v = g->v; a.o = g->o; a.lse = static_cast<float*>(g->l_out);
+    a.bh = g->batch_heads; a.sl = g->seq_len; a.hd = g->head_dim; a.causal = g->causal; a.window = g->window;
+    a.scale = g->scale; a.v_descale = (g->v_descale == 0.0f) ? 1.0f : g->v_descale;
+    a.scale_q_dev = g->scale_q_dev; a.scale_k_dev = g->scale_k_dev; a.scale_v_dev = g->scale_v_dev;
+    a.v16_workspace = g_noalloc_ptr[dev];
+    a.stream = reinterpret_cast<cudaStream_t>(g->stream);
+    e = launch(a);
+    if (e != cudaSuccess) {
+        if (err && err_len > 0) snprintf(err, (size_t)err_len, "fa_forward_noalloc: launch: %s", cudaGetErrorString(e));
+        return FA_ERR_CUDA;
+    }
+    return FA_OK;
+}

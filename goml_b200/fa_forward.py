@@ -104,6 +104,8 @@ def FALoad():
                 lib.fa_kernel_name.argtypes = [i]
                 lib.fa_forward_ex.restype = i
                 lib.fa_forward_ex.argtypes = [p, C.POINTER(ForwardArgs)]
+                lib.fa_forward_noalloc.restype = i
+                lib.fa_forward_noalloc.argtypes = [C.POINTER(ForwardArgs), C.c_char_p, i]
                 lib.fa_device_status.restype = i
                 lib.fa_device_status.argtypes = [p]
                 _lib = lib
@@ -184,6 +186,23 @@ class FAContext:
 
     def __exit__(self, *exc):
         self.Destroy()
+
+
+NOALLOC_MAX_ELEMS = 16 << 20
+
+
+def FAForwardNoAlloc(q, k, v, o, lOut, bh, sl, hd, causal, window, scale, v_descale=1.0,
+                     scale_q_dev=0, scale_k_dev=0, scale_v_dev=0, stream=0) -> None:
+    """Attention forward for callers that may not allocate (frameworks that reserved the whole
+    GPU, frozen-memory-map processes): scratch is a fixed 32 MiB array inside the library, so
+    bh*sl*hd must not exceed NOALLOC_MAX_ELEMS.  No context is needed.  Calls that overlap on
+    the GPU share (and race on) that array; make the first call on a device before any capture."""
+    a = ForwardArgs(q, k, v, o, lOut or None, bh, sl, hd, causal, window, scale, v_descale,
+                    scale_q_dev or None, scale_k_dev or None, scale_v_dev or None, stream or None)
+    buf = C.create_string_buffer(256)
+    st = FALoad().fa_forward_noalloc(C.byref(a), buf, len(buf))
+    if st != FA_OK:
+        raise FAError("fa_forward_noalloc", st, buf.value.decode(errors="replace"))
 
 
 def FACreate() -> FAContext:

@@ -147,6 +147,22 @@ typedef struct {
 
 FA_API fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* args);
 
+/* No counterpart in the reference: an attention forward that allocates nothing.
+ * The other entry points draw their scratch (an fp16 copy of V, 2*BH*S*D bytes) from a
+ * memory pool.  This one is for callers that may not touch the allocator at all — code
+ * embedded in a framework that reserved the whole GPU up front and forbids later
+ * cudaMalloc-family calls, or real-time / safety-certified processes whose device memory
+ * map is frozen after start-up.  Its scratch is a fixed 32 MiB device array inside the
+ * library (held by every GPU that loads it, until exit), so one call is limited to
+ *     batch_heads * seq_len * head_dim <= 16 Mi (16 777 216) elements;
+ * larger problems return FA_ERR_UNSUPPORTED_SHAPE with a message (split the batch, or use
+ * fa_forward_ex).  Arguments and results are those of fa_forward_ex (same kernels); no
+ * context is needed.  err/err_len: optional caller buffer that receives a message on failure.
+ * The array is shared by all calls on a GPU: calls whose GPU work overlaps race on it — use
+ * one stream or serialise.  The first call on each device performs a one-time set-up
+ * (device address of the array, kernel attributes); make it before any stream capture. */
+FA_API fa_status_t fa_forward_noalloc(const fa_forward_args_t* args, char* err, int err_len);
+
 /* Synchronises the context's device and reports whether any attention kernel
  * recorded a bounded-wait expiry since the last call: FA_OK, or FA_ERR_INTERNAL
  * with the code in fa_last_cuda_error. */
