@@ -161,14 +161,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + C::OFF_BAR;
+    // Completion barriers are indexed by ring stage (block j -> j % STAGES) and double as the
+    // "stage free" signals of the K and V rings: one tcgen05.commit per MMA batch instead of two.
     const uint32_t bar_q = bars;
-    const uint32_t bar_kfull = bars + 8;                  // [STAGES]
-    const uint32_t bar_kempty = bar_kfull + 8 * STAGES;   // [STAGES]
-    const uint32_t bar_vfull = bar_kempty + 8 * STAGES;   // [STAGES]
-    const uint32_t bar_vempty = bar_vfull + 8 * STAGES;   // [STAGES]
-    const uint32_t bar_sfull = bar_vempty + 8 * STAGES;   // [2] S[b] = Q K^T complete (and every earlier MMA)
-    const uint32_t bar_pfull = bar_sfull + 16;            // [2] softmax wrote P into S[b] (and rescaled O if needed)
-    const uint32_t bar_pvdone = bar_pfull + 16;           // [2] O += P V of a block using S[b] complete
+    const uint32_t bar_kfull = bars + 8;                  // [STAGES] K tile landed
+    const uint32_t bar_vfull = bar_kfull + 8 * STAGES;    // [STAGES] V tile landed
+    const uint32_t bar_sfull = bar_vfull + 8 * STAGES;    // [STAGES] S = Q K^T of that block complete (K stage reusable)
+    const uint32_t bar_pvdone = bar_sfull + 8 * STAGES;   // [STAGES] O += P V of that block complete (V stage reusable)
+    const uint32_t bar_pfull = bar_pvdone + 8 * STAGES;   // [2] softmax wrote P into S[b] (and rescaled O if needed)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 240);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -192,15 +192,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         mbar_init(bar_q, 1);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(bar_kfull + 8 * s, 1);
-            mbar_init(bar_kempty + 8 * s, 1);
             mbar_init(bar_vfull + 8 * s, 1);
-            mbar_init(bar_vempty + 8 * s, 1);
+            mbar_init(bar_sfull + 8 * s, 1);
+            mbar_init(bar_pvdone + 8 * s, 1);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(bar_sfull + 8 * b, 1);
-            mbar_init(bar_pfull + 8 * b, NUM_SOFTMAX_WARPS * 32);
-            mbar_init(bar_pvdone + 8 * b, 1);
-        }
+        for (int b = 0; b < 2; b++) mbar_init(bar_pfull + 8 * b, NUM_SOFTMAX_WARPS * 32);
         *abort_flag = (sbase & 1023u) ? ST_BAD_SMEM_ALIGN : 0u;
         fence_mbar_init();
     }
@@ -230,10 +226,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             uint32_t ph = 1;  // "previous phase complete": the rings start empty
             for (int j = 0; j < nblk; j++) {
                 const int key0 = (blk0 + j) * BN;
-                if (!mbar_wait(bar_kempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                if (!mbar_wait(bar_sfull + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;   // Q K^T three blocks back is done
                 mbar_arrive_expect_tx(bar_kfull + 8 * s, C::K_BYTES);
                 tma_load_3d(sbase + C::OFF_K + s * C::K_BYTES, &tmap_k, bar_kfull + 8 * s, 0, key0, head);
-                if (!mbar_wait(bar_vempty + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;
+                if (!mbar_wait(bar_pvdone + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;  // P V three blocks back is done
                 mbar_arrive_expect_tx(bar_vfull + 8 * s, C::V_BYTES);
 #pragma unroll
                 for (int h = 0; h < HD / 64; h++)  // one 64-column (128-byte) slab of d per copy
@@ -261,8 +257,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 #pragma unroll
                 for (int k = 0; k < HD / 32; k++)
                     mma_f8f6f4_ss(tmem_s + (j & 1) * BN, qd + 2 * k, kd + 2 * k, idesc_qk, k != 0);
-                mma_commit(bar_kempty + 8 * ks);
-                mma_commit(bar_sfull + 8 * (j & 1));
+                mma_commit(bar_sfull + 8 * ks);
                 if (++ks == STAGES) { ks = 0; kph ^= 1; }
             };
             ok = mbar_wait(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
@@ -281,8 +276,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     const uint64_t vd = mnmajor_desc_sw128(vaddr + k * 16 * 128, C::V_HALF_BYTES);
                     mma_f16_ts(tmem_o, tmem_s + b * BN + 8 * k, vd, idesc_pv, (j | k) != 0);
                 }
-                mma_commit(bar_vempty + 8 * vs);
-                mma_commit(bar_pvdone + 8 * b);
+                mma_commit(bar_pvdone + 8 * vs);
                 if (++vs == STAGES) { vs = 0; vph ^= 1; }
                 TRACE(1, j, 2);
                 // S[b] is rewritten by the Q K^T two blocks ahead; it is issued behind this P V on the
@@ -307,6 +301,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         float m_ref = -INFINITY;                 // reference max used in the exponent (log2 units)
         float l = 0.f;                           // running sum of P * 2^POFF
         bool ok = true;
+        int rs = 0;           // ring stage of block j (j % STAGES) and its phase; those of block j-1
+        uint32_t rph = 0;
+        int rs_prev = 0;
+        uint32_t rph_prev = 0;
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
 
@@ -314,7 +312,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const int key0 = (blk0 + j) * BN;
             TRACE(0, j, 0);
             const int b = j & 1;
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * b, (j >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * rs, rph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
             TRACE(0, j, 1);
             tc_fence_after();
             uint32_t sreg[BN];
@@ -353,7 +351,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const float m_new = bump ? mx : m_ref;
             if (j > 0 && __any_sync(0xffffffffu, bump)) {
                 // O is final only once the previous P V has finished
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * rs_prev, rph_prev, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
                 tc_fence_after();
                 const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
                 l *= f;
@@ -394,10 +392,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             tc_fence_before();
             mbar_arrive(bar_pfull + 8 * b);
             TRACE(0, j, 7);
+            rs_prev = rs;
+            rph_prev = rph;
+            if (++rs == STAGES) { rs = 0; rph ^= 1; }
         }
 
         // epilogue: O / l (times the V dequantisation scale) -> fp16
-        if (ok && __all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * ((nblk - 1) & 1), ((nblk - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_SOFTMAX))) {
+        if (ok && __all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * rs_prev, rph_prev, abort_flag, ST_TIMEOUT_SOFTMAX))) {
             tc_fence_after();
             const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
             const float inv = (l > 0.f) ? vds / l : 0.f;
