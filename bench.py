@@ -36,8 +36,8 @@ GEMM = dict(M=8192, N=8192, K=8192)
 NOMINAL_FP8_TFLOPS = 4500.0
 FALLBACK_BF16_TFLOPS = 1590.0  # profiling-recipe fallback when MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel at the bench
-# shape, from the ncu capture summarised under profiles/ (None until a capture exists)
-ATTN_DRAM_TRAFFIC_BYTES = None
+# shape, from the ncu capture summarised in profiles/fa_fwd_hd128_bh32_s8192.md
+ATTN_DRAM_TRAFFIC_BYTES = 4 * (134.27e6 + 41.31e6)  # 4 x the BH=32 capture (traffic grows with the number of heads)
 
 
 def att_flops(a):
@@ -71,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -197,8 +197,8 @@ def workload_config(n, workload):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="both", choices=["both", "attn", "gemm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
