@@ -13,7 +13,7 @@
 //        128-bit stores while the next tile's main loop already runs.
 //
 // One persistent CTA per SM walks output tiles in an order that keeps a band of
-// A rows and a few B panels resident in L2.  No multicast, no clusters.
+// A rows and a few B panels resident in L2.  Every CTA loads its own tiles; no thread-block clusters.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>

@@ -5,7 +5,7 @@
 // Conventions used by every kernel in this directory:
 //  * every wait on an mbarrier is bounded; when the bound is hit the waiter
 //    records a status word and the CTA drains and exits (no trap, no hang);
-//  * no TMA load carries a cluster-multicast qualifier;
+//  * every CTA issues its own TMA loads from its own GPU (no cross-CTA broadcast loads);
 //  * shared-memory operand tiles are written by TMA with 128-byte (or 64-byte)
 //    swizzle and described to the tensor core with the matching layout type.
 #pragma once
