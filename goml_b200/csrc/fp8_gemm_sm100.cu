@@ -28,16 +28,24 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;          // rows of C per tile (= TMEM lanes)
-constexpr int BN = 256;          // columns of C per tile (= TMEM columns per buffer)
 constexpr int BK = 128;          // K bytes per pipeline stage (one 128-byte swizzle span)
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;
-constexpr int B_BYTES = BN * BK;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int TMEM_COLS = 512;    // 2 accumulator buffers x 256 fp32 columns
 constexpr int GROUP_M = 16;       // tile-order band height (in tiles)
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+// Tile width BN (columns of C per tile = TMEM columns per accumulator buffer).  256 is the
+// tensor-efficient shape (the MMA reads (128+BN)*32 operand bytes per BN/2 clocks, within the
+// 128 B/clk shared-memory read rate only for BN >= 128); 128 and 64 exist so that small and
+// skinny problems (few 128x256 tiles) still spread over all SMs — those are HBM/latency-bound,
+// and a narrower tile leaves room for a deeper TMA ring.
+template <int BN>
+struct Tile {
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers (a power of two >= 32)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
 
 enum : uint32_t {
     ST_OK = 0,
@@ -77,9 +85,13 @@ __device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmParams p) {
+    constexpr int STAGES = Tile<BN>::STAGES;
+    constexpr int STAGE_BYTES = Tile<BN>::STAGE_BYTES;
+    constexpr int TMEM_COLS = Tile<BN>::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle atom = 8 rows x 128 B)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -278,28 +290,46 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
         if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return (int)e;
         if (major != 10) return (int)cudaErrorNoKernelImageForDevice;
         if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      SMEM_BYTES)) != cudaSuccess)
-            return (int)e;
+        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<256>::SMEM_BYTES)) != cudaSuccess) return (int)e;
+        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<128>::SMEM_BYTES)) != cudaSuccess) return (int)e;
+        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<64>::SMEM_BYTES)) != cudaSuccess) return (int)e;
         st.num_sms = sms;
         st.ready = true;
     }
 
+    // Tile width: 256 unless a narrower tile cuts (waves x per-k-block MMA time) by more than a quarter —
+    // i.e. only when the 128x256 tiling leaves most SMs idle (small or skinny problems).  Per-k-block MMA
+    // time: 128 / 64 / 48 clocks for BN = 256 / 128 / 64 (the last one limited by operand reads).
+    const long long m_tiles = (M + BM - 1) / BM;
+    auto estimate = [&](int width, int clocks) {
+        const long long tiles = m_tiles * ((N + width - 1) / width);
+        return ((tiles + st.num_sms - 1) / st.num_sms) * clocks;
+    };
+    int bn = 256;
+    long long best = estimate(256, 128) * 3 / 4;
+    if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
+    if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
+
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
-    p.m_tiles = (M + BM - 1) / BM;
-    p.n_tiles = (N + BN - 1) / BN;
+    p.m_tiles = (int)m_tiles;
+    p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
 
     CUtensorMap ta, tb;
     if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B))
+        !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint32_t)bn, BK, CU_TENSOR_MAP_SWIZZLE_128B))
         return (int)cudaErrorInvalidValue;
 
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     const int grid = (int)(tiles < st.num_sms ? tiles : st.num_sms);
-    fp8_gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, p);
+    else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, p);
+    else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, p);
     return (int)cudaGetLastError();
 }
 
