@@ -1,0 +1,169 @@
+"""FP8 dispatch of goml's nn call sites for one Llama-style decoder block (prefill).
+
+goml's `nn.Linear.Forward` (nn/linear.go:53-74), `nn.FeedForward.forwardSwiGLU`
+(nn/feedforward.go:54-79: W2(silu(W1 x) * W3 x)) and `nn.MultiHeadAttention.Forward`
+(nn/attention.go:60-160) run in F32 today.  Here every projection goes through the FP8
+GEMM library, the attention through the FP8 attention library and every quantisation
+through the quantiser library — scales stay on the device between them (no host round
+trip).  The glue that is not on the hot path (RMSNorm with eps inside the square root,
+half-split RoPE, SiLU gate, residual adds, layout permutes: the arithmetic of
+internal/abjexam/llama_hf_f64ref.go:126-178 and battle_a_llm_f64ref.go:182-237) runs as
+plain fp32 torch ops on the same stream.
+
+torch tensors are used as device buffers; all heavy kernels are reached through the C ABI.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import fa_forward as F, fp8_gemm as G, quantize as Q
+
+
+class FP8Tensor:
+    """e4m3 codes + a one-float device scale (and the amax word the quantiser writes)."""
+
+    def __init__(self, codes: torch.Tensor, scale_amax: torch.Tensor):
+        self.codes = codes
+        self.sa = scale_amax  # [scale, amax] fp32 on the device
+
+    @property
+    def scale_ptr(self) -> int:
+        return self.sa.data_ptr()
+
+
+def quantize(x: torch.Tensor, unit: bool = False) -> FP8Tensor:
+    """Per-tensor FP32 -> e4m3 through libfp8quant (scale = amax/448, or amax when unit)."""
+    x = x.contiguous()
+    assert x.dtype == torch.float32 and x.is_cuda
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    sa = torch.zeros(2, dtype=torch.float32, device=x.device)
+    fn = Q.QuantizeF32ToF8E4M3Unit if unit else Q.QuantizeF32ToF8E4M3
+    fn(x.data_ptr(), codes.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, x.numel(), torch.cuda.current_stream().cuda_stream)
+    return FP8Tensor(codes, sa)
+
+
+class FP8Linear:
+    """y = x W^T with W [out, in] (the layout of nn/linear.go:14), both operands e4m3, bf16 result."""
+
+    def __init__(self, weight: torch.Tensor):
+        self.out_features, self.in_features = weight.shape
+        self.w = quantize(weight.float())
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        M = x.numel() // self.in_features
+        xq = quantize(x.reshape(M, self.in_features).float())
+        y = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=x.device)
+        G.FP8GEMMScaled(M, self.out_features, self.in_features, xq.codes.data_ptr(), self.w.codes.data_ptr(), y.data_ptr(),
+                        1.0, xq.scale_ptr, self.w.scale_ptr, G.OutBF16, torch.cuda.current_stream().cuda_stream)
+        return y
+
+
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    return gamma * x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def rope_half_split(x: torch.Tensor, theta: float) -> torch.Tensor:
+    """x [B, H, S, hd]: pairs (i, i + hd/2), angle = pos * theta^(-2i/hd)."""
+    hd, S = x.shape[-1], x.shape[-2]
+    half = hd // 2
+    freq = theta ** (-2.0 * torch.arange(half, device=x.device, dtype=torch.float64) / hd)
+    ang = torch.arange(S, device=x.device, dtype=torch.float64)[:, None] * freq[None, :]
+    c, s = ang.cos().float(), ang.sin().float()
+    x0, x1 = x[..., :half], x[..., half:]
+    return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+
+
+class FP8DecoderBlock:
+    """Llama-style block: RMSNorm -> QKV -> RoPE -> causal FP8 attention -> O -> residual -> RMSNorm -> SwiGLU -> residual."""
+
+    def __init__(self, d_model, n_heads, ffn_hidden, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0):
+        self.d, self.H, self.F = d_model, n_heads, ffn_hidden
+        self.hd = d_model // n_heads
+        assert self.hd in (64, 128)
+        self.qkv, self.o = FP8Linear(wqkv), FP8Linear(wo)
+        self.gate_up, self.down = FP8Linear(wgate_up), FP8Linear(wdown)
+        self.norm1, self.norm2 = norm1.float(), norm2.float()
+        self.eps, self.theta = eps, theta
+        self.fa = F.FACreate()
+
+    def attention(self, xn: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        H, hd = self.H, self.hd
+        qkv = self.qkv(xn).float().view(B, S, 3, H, hd).permute(2, 0, 3, 1, 4)  # [3, B, H, S, hd]
+        q = rope_half_split(qkv[0], self.theta)
+        k = rope_half_split(qkv[1], self.theta)
+        qq, kq, vq = quantize(q), quantize(k), quantize(qkv[2])
+        o = torch.empty((B * H, S, hd), dtype=torch.float16, device=xn.device)
+        self.fa.ForwardEx(qq.codes.data_ptr(), kq.codes.data_ptr(), vq.codes.data_ptr(), o.data_ptr(), 0, B * H, S, hd, 1, 0,
+                          1.0 / math.sqrt(hd), 1.0, qq.scale_ptr, kq.scale_ptr, vq.scale_ptr, torch.cuda.current_stream().cuda_stream)
+        return o.view(B, H, S, hd).permute(0, 2, 1, 3).reshape(B * S, H * hd)
+
+    def __call__(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """x [B*S, d] fp32 -> [B*S, d] fp32."""
+        x = x.float()
+        x = x + self.o(self.attention(rms_norm(x, self.norm1, self.eps), B, S)).float()
+        gu = self.gate_up(rms_norm(x, self.norm2, self.eps)).float()
+        g, u = gu[:, : self.F], gu[:, self.F:]
+        x = x + self.down(torch.nn.functional.silu(g) * u).float()
+        return x
+
+    def close(self):
+        self.fa.Destroy()
+
+
+def _main():
+    """Times the full-size block config: d_model 4096, 32 heads x 128, SwiGLU hidden 11008, B=8 x S=2048
+    tokens, random-init weights N(0, 0.02), embeddings N(0, 1) — the whole block and its FP8 kernels alone."""
+    import sys
+    B, S, d, H, Fh = 8, 2048, 4096, 32, 11008
+    if len(sys.argv) > 1:
+        B = int(sys.argv[1])
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(4)
+    rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device=dev) * std
+    blk = FP8DecoderBlock(d, H, Fh, rn(3 * d, d), rn(d, d), rn(2 * Fh, d), rn(d, Fh), torch.ones(d, device=dev), torch.ones(d, device=dev))
+    x = rn(B * S, d, std=1.0)
+
+    def timed(fn, iters=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    total = timed(lambda: blk(x, B, S))
+    M = B * S
+    # kernels alone, on pre-quantised operands
+    xq = quantize(x)
+    sh = torch.cuda.current_stream().cuda_stream
+
+    def gemm(lin, a):
+        y = torch.empty((M, lin.out_features), dtype=torch.bfloat16, device=dev)
+        return timed(lambda: G.FP8GEMMScaled(M, lin.out_features, lin.in_features, a.codes.data_ptr(), lin.w.codes.data_ptr(),
+                                             y.data_ptr(), 1.0, a.scale_ptr, lin.w.scale_ptr, G.OutBF16, sh))
+
+    hq = quantize(rn(M, Fh, std=1.0))
+    t_qkv, t_o, t_gu, t_dn = gemm(blk.qkv, xq), gemm(blk.o, xq), gemm(blk.gate_up, xq), gemm(blk.down, hq)
+    hd = d // H
+    q3 = [quantize(rn(B * H, S, hd, std=1.0)) for _ in range(3)]
+    o = torch.empty((B * H, S, hd), dtype=torch.float16, device=dev)
+    t_att = timed(lambda: blk.fa.ForwardEx(q3[0].codes.data_ptr(), q3[1].codes.data_ptr(), q3[2].codes.data_ptr(), o.data_ptr(), 0,
+                                           B * H, S, hd, 1, 0, 1 / math.sqrt(hd), 1.0, q3[0].scale_ptr, q3[1].scale_ptr, q3[2].scale_ptr, sh))
+    fl_gemm = 2.0 * M * d * (3 * d + d + 3 * Fh)
+    fl_att = 2.0 * B * H * S * S * hd
+    kern = t_qkv + t_o + t_gu + t_dn + t_att
+    print(f"block B={B} S={S} d={d} H={H} F={Fh}: total {total:.3f} ms; FP8 kernels {kern:.3f} ms "
+          f"(qkv {t_qkv:.3f}, o {t_o:.3f}, gate+up {t_gu:.3f}, down {t_dn:.3f}, attention {t_att:.3f}); glue+quantise {total - kern:.3f} ms")
+    print(f"GEMM {fl_gemm / (t_qkv + t_o + t_gu + t_dn) / 1e9:.0f} TFLOPS over {fl_gemm / 1e12:.2f} TFLOP; "
+          f"attention (causal) {fl_att / t_att / 1e9:.0f} TFLOPS; whole block {(fl_gemm + fl_att) / total / 1e9:.0f} TFLOPS")
+    blk.close()
+
+
+if __name__ == "__main__":
+    _main()

@@ -1,0 +1,64 @@
+"""CPU restatement (numpy, fp64) of one Llama-style decoder block with the FP8 quantisation points
+of the product chain.  TEST INFRASTRUCTURE ONLY.
+
+Arithmetic follows internal/abjexam/llama_hf_f64ref.go:94-178 (pre-norm block, y = x W^T with W [out,in],
+[S,H,hd] -> [H,S,hd], causal attention, SwiGLU silu(gate)*up, residuals) with the primitives of
+internal/abjexam/battle_a_llm_f64ref.go:182-194 (rmsNorm: eps inside the square root) and :221-237
+(half-split RoPE: pairs (i, i+hd/2), angle = pos * theta^(-2i/hd)).  Every GEMM operand and Q/K/V are
+quantised per tensor to e4m3 (scale = amax/448) exactly where the product quantises; GEMM results are
+rounded to bf16 and the attention output to fp16, as the libraries return them.
+"""
+import math
+
+import numpy as np
+
+import oracle as O
+
+
+def _linear(x, w):
+    """bf16( sx*sw * codes(x) . codes(w)^T ), fp64 accumulation."""
+    xq, sx, _ = O.quantize_f32(x.astype(np.float32))
+    wq, sw, _ = O.quantize_f32(w.astype(np.float32))
+    alpha = float(np.float32(sx) * np.float32(sw))  # the kernel multiplies the fp32 scales
+    return O.round_bf16(O.gemm_f64(xq, wq, alpha)).astype(np.float64)
+
+
+def _rms_norm(x, gamma, eps):
+    return gamma * x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+
+
+def _rope(x, theta):  # x [B, H, S, hd]
+    hd, S = x.shape[-1], x.shape[-2]
+    half = hd // 2
+    freq = theta ** (-2.0 * np.arange(half) / hd)
+    ang = np.arange(S)[:, None] * freq[None, :]
+    c, s = np.cos(ang), np.sin(ang)
+    x0, x1 = x[..., :half], x[..., half:]
+    return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1)
+
+
+def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0, intermediates=None):
+    """Returns the block output [B*S, d] (fp64).  When `intermediates` is a dict it receives the input of
+    every quantised stage and that stage's output, so each product stage can be checked on identical inputs."""
+    x = x.astype(np.float64)
+    d = x.shape[1]
+    hd = d // H
+    Fh = wdown.shape[1]
+    keep = intermediates if intermediates is not None else {}
+    keep["xn1"] = _rms_norm(x, norm1, eps)
+    keep["qkv"] = _linear(keep["xn1"], wqkv)
+    qkv = keep["qkv"].reshape(B, S, 3, H, hd).transpose(2, 0, 3, 1, 4)
+    q, k, v = _rope(qkv[0], theta), _rope(qkv[1], theta), qkv[2]
+    (qq, sq, _), (kq, sk, _), (vq, sv, _) = [O.quantize_f32(np.ascontiguousarray(t, np.float32).reshape(B * H, S, hd)) for t in (q, k, v)]
+    scale = float(np.float32(1.0 / math.sqrt(hd)) * np.float32(sq) * np.float32(sk))
+    o, _ = O.attention_f64(qq, kq, vq, 1, 0, scale, float(sv))
+    keep["attn"] = O.round_fp16(o).astype(np.float64).reshape(B, H, S, hd).transpose(0, 2, 1, 3).reshape(B * S, d)
+    keep["ao"] = _linear(keep["attn"], wo)
+    x = x + keep["ao"]
+    keep["x_mid"] = x
+    keep["xn2"] = _rms_norm(x, norm2, eps)
+    keep["gu"] = _linear(keep["xn2"], wgate_up)
+    g, u = keep["gu"][:, :Fh], keep["gu"][:, Fh:]
+    keep["h"] = g / (1.0 + np.exp(-g)) * u
+    keep["ffn"] = _linear(keep["h"], wdown)
+    return x + keep["ffn"]
