@@ -153,6 +153,12 @@ __global__ void __launch_bounds__(256) v_to_f16_kernel(const uint4* __restrict__
     }
 }
 
+// Sign flip of one row of raw scores for a negative scale (the row max is taken on sign-adjusted scores).
+// Rare, so it is kept out of line: the common path pays one not-taken branch instead of 64 predicated ops.
+__device__ __noinline__ void negate_scores(uint32_t* s) {
+    for (int c = 0; c < BN; c++) s[c] ^= 0x80000000u;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -321,14 +327,21 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             tmem_ld_wait();
             TRACE(0, j, 2);
 
-            if (neg) {
+            if (neg) {  // out of line, on a local copy so that sreg stays in registers
+                uint32_t tmp[BN];
 #pragma unroll
-                for (int c = 0; c < BN; c++) sreg[c] ^= 0x80000000u;
+                for (int c = 0; c < BN; c++) tmp[c] = sreg[c];
+                negate_scores(tmp);
+#pragma unroll
+                for (int c = 0; c < BN; c++) sreg[c] = tmp[c];
             }
             // does this block need per-element masking?  (uniform across the CTA)
             const bool mask_blk = (key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
                                   (p.window > 0 && key0 < q0 + BM - p.window);
             if (mask_blk) {
+                // the empty volatile statement keeps this a real (in the common case not-taken) branch
+                // instead of 64 predicated selects executed for every block
+                asm volatile("" ::: "memory");
 #pragma unroll
                 for (int c = 0; c < BN; c++) {
                     const int key = key0 + c;

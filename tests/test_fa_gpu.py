@@ -84,6 +84,18 @@ def test_ragged_masks_windows(fa_ctx, bh, sl, hd, ca, w):
     check(o, ref, lse, lref)
 
 
+@pytest.mark.parametrize("scale_sign", [-1.0, 0.0])
+def test_negative_and_zero_scale(fa_ctx, scale_sign):
+    # the scale is a free float in the ABI: a negative one reverses the ranking of the keys, zero gives uniform weights
+    bh, sl, hd = 2, 300, 128
+    (q, sq, _), (k, sk, _), (v, sv, _) = [O.quantize_f32(O.seeded_normal(n, (bh, sl, hd), config="negscale"), 0) for n in "QKV"]
+    scale = scale_sign * float(sq) * float(sk) / math.sqrt(hd)
+    for causal in (0, 1):
+        o, lse = run_attention(fa_ctx, q, k, v, causal, 0, scale, v_descale=float(sv), entry="ex")
+        ref, lref = O.attention_f64(q, k, v, causal, 0, scale, float(sv))
+        check(o, ref, lse, lref)
+
+
 def test_lse_uniform_and_layout(fa_ctx):
     # backend/cuda/fa_forward_test.go:112-189 and :191-288
     bh, sl, hd = 3, 280, 128
