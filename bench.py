@@ -292,10 +292,13 @@ def main():
     if G.device_status() != 0:
         raise SystemExit("bench.py: the GEMM kernel reported a bounded-wait expiry")
 
-    # ---- end to end through the public API with HOST buffers (pinned), copies inside the timed region
-    e2e_steps = max(2, min(args.steps, 5))
+    # ---- end to end through the public API with HOST buffers (pinned): every step copies its inputs host->device
+    # and its results device->host inside the timed region.  The caller-side pattern is the usual one for a
+    # pointer-based ABI: three streams (copy-in, compute, copy-out) over double-buffered device tensors, so the
+    # copies of neighbouring steps overlap the kernels; each step still moves all of its own bytes.
+    e2e_steps = max(4, min(args.steps, 10))
     h2d = d2h = 0
-    host = {}
+    host, devbuf = {}, [{}, {}]
     if do_attn:
         for name, t in (("q", q), ("k", k), ("v", v)):
             host[name] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
@@ -303,29 +306,58 @@ def main():
         host["o"] = torch.empty(o.shape, dtype=o.dtype, pin_memory=True)
         host["lse"] = torch.empty(lse.shape, dtype=lse.dtype, pin_memory=True)
         d2h += o.numel() * 2 + lse.numel() * 4
+        devbuf[0].update(q=q, k=k, v=v, o=o, lse=lse)
+        devbuf[1].update({n: torch.empty_like(t) for n, t in devbuf[0].items() if n in ("q", "k", "v", "o", "lse")})
     if do_gemm:
         host["a"] = torch.empty(a.shape, dtype=a.dtype, pin_memory=True).copy_(a)   # activations travel; the weight B stays resident
         host["c"] = torch.empty(c.shape, dtype=c.dtype, pin_memory=True)
         h2d += a.numel()
         d2h += c.numel() * 2
+        devbuf[0].update(a=a, c=c)
+        devbuf[1].update(a=torch.empty_like(a), c=torch.empty_like(c))
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]     # inputs of buffer b are on the device
+    ev_comp = [torch.cuda.Event() for _ in range(2)]   # kernels of buffer b have finished
+    ev_out = [torch.cuda.Event() for _ in range(2)]    # results of buffer b are on the host
 
-    def e2e_step():
+    def e2e_step(i):
+        b = i & 1
+        d = devbuf[b]
+        with torch.cuda.stream(s_in):
+            if i >= 2: s_in.wait_event(ev_comp[b])       # the kernels that read this input buffer two steps ago are done
+            if do_attn:
+                d["q"].copy_(host["q"], non_blocking=True); d["k"].copy_(host["k"], non_blocking=True); d["v"].copy_(host["v"], non_blocking=True)
+            if do_gemm:
+                d["a"].copy_(host["a"], non_blocking=True)
+            ev_in[b].record(s_in)
+        stream.wait_event(ev_in[b])
+        if i >= 2: stream.wait_event(ev_out[b])          # the results written two steps ago have been read out
         if do_attn:
-            q.copy_(host["q"], non_blocking=True); k.copy_(host["k"], non_blocking=True); v.copy_(host["v"], non_blocking=True)
-            attn()
-            host["o"].copy_(o, non_blocking=True); host["lse"].copy_(lse, non_blocking=True)
+            ctx.ForwardEx(d["q"].data_ptr(), d["k"].data_ptr(), d["v"].data_ptr(), d["o"].data_ptr(), d["lse"].data_ptr(), bh, sl, hd,
+                          ATT["causal"], 0, softmax_scale, 1.0, sp, sp + 8, sp + 16, sh)
         if do_gemm:
-            a.copy_(host["a"], non_blocking=True)
-            gemm()
-            host["c"].copy_(c, non_blocking=True)
+            G.FP8GEMMScaled(M, N, K, d["a"].data_ptr(), b_ptr, d["c"].data_ptr(), 1.0, sp + 24, sp + 32, G.OutBF16, sh)
+        ev_comp[b].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[b])
+            if do_attn:
+                host["o"].copy_(d["o"], non_blocking=True); host["lse"].copy_(d["lse"], non_blocking=True)
+            if do_gemm:
+                host["c"].copy_(d["c"], non_blocking=True)
+            ev_out[b].record(s_out)
 
-    e2e_step(); torch.cuda.synchronize()
+    b_ptr = b.data_ptr() if do_gemm else 0
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
     barrier(); torch.cuda.synchronize()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record(stream)
+    e0.record(s_in)
+    stream.wait_event(e0); s_out.wait_event(e0)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    s_out.wait_stream(stream); s_out.wait_stream(s_in)
+    e1.record(s_out)
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
