@@ -1,0 +1,340 @@
+// goml_cuda.hpp — C++ host side above the C ABI, mirroring goml's Go package backend/cuda for this path.
+//
+// goml binds its CUDA libraries without cgo: `purego.Dlopen` + `RegisterLibFunc`
+// (backend/cuda/fp8_gemm.go:27-41, backend/cuda/fa_forward.go:74-115) behind a library search
+// (backend/cuda/arch.go:57-101).  This header does the same with dlopen/dlsym and keeps the names,
+// argument meaning and error text of that package:
+//
+//   LibsDir / resolveLib                      arch.go:63-101
+//   FP8GEMM(M,N,K,A,B,C,mode,stream)          fp8_gemm.go:52-62     ("fp8_gemm: CUDA error %d")
+//   FALoad / FACreate / FAContext::ForwardTrain / Destroy / FAVersion / FAStatus strings
+//                                             fa_forward.go:25-215  ("fa_forward_train: <status> (<message>)")
+//   QuantizeF32ToF8E4M3 / ...Unit             the calls of internal/abjexam/battle_a_llm.go:476-494
+// plus what goml lacks: the additive entry points (FP8GEMMScaled, ForwardEx) and a multi-GPU manager
+// (one context + one stream per device; contiguous head / row-tile partitions).
+//
+// Pointers are raw device addresses (uintptr_t), as in the Go bindings.  Errors are thrown as
+// goml::cuda::Error.  Header-only; link with -ldl and the CUDA runtime (for the device manager).
+#pragma once
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/fa_sm120.h"
+
+namespace goml {
+namespace cuda {
+
+struct Error : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+namespace detail {
+inline bool is_dir(const std::string& p) { struct stat st; return !p.empty() && stat(p.c_str(), &st) == 0 && S_ISDIR(st.st_mode); }
+inline bool is_file(const std::string& p) { struct stat st; return !p.empty() && stat(p.c_str(), &st) == 0 && S_ISREG(st.st_mode); }
+inline std::string env(const char* k) { const char* v = getenv(k); return v ? v : ""; }
+inline std::string exe_dir() {
+    char buf[4096];
+    ssize_t n = readlink("/proc/self/exe", buf, sizeof(buf) - 1);
+    if (n <= 0) return "";
+    buf[n] = 0;
+    std::string s(buf);
+    return s.substr(0, s.find_last_of('/'));
+}
+template <class Fn>
+Fn sym(void* lib, const char* name) {
+    void* p = dlsym(lib, name);
+    if (!p) throw Error(std::string("dlsym ") + name + ": " + dlerror());
+    return reinterpret_cast<Fn>(p);
+}
+}  // namespace detail
+
+// Directory searched for the prebuilt libraries.  Priority (arch.go:57-82): $GOML_LIBS_DIR, ./libs,
+// <executable dir>/libs, /usr/local/lib/goml; the first existing directory wins; "" if none.
+inline std::string LibsDir() {
+    char cwd[4096];
+    std::vector<std::string> c = {detail::env("GOML_LIBS_DIR")};
+    if (getcwd(cwd, sizeof(cwd))) c.push_back(std::string(cwd) + "/libs");
+    if (!detail::exe_dir().empty()) c.push_back(detail::exe_dir() + "/libs");
+    c.push_back("/usr/local/lib/goml");
+    for (const auto& d : c)
+        if (detail::is_dir(d)) return d;
+    return "";
+}
+// Full path when the file exists in LibsDir(), else the bare name for the OS loader (arch.go:84-101).
+inline std::string resolveLib(const std::string& name) {
+    const std::string d = LibsDir();
+    if (!d.empty() && detail::is_file(d + "/" + name)) return d + "/" + name;
+    return name;
+}
+
+// ------------------------------------------------------------------------------------ FP8 GEMM
+enum { ModeOriginal = 0, ModeSinglesync = 1 };
+enum { FP8OutFP16 = 0, FP8OutBF16 = 1 };
+
+namespace detail {
+struct GemmLib {
+    void* lib = nullptr;
+    int (*gemm)(int, int, int, const void*, const void*, void*, int, void*) = nullptr;
+    int (*original)(int, int, int, const void*, const void*, void*, void*) = nullptr;
+    int (*ss)(int, int, int, const void*, const void*, void*, void*) = nullptr;
+    int (*scaled)(int, int, int, const void*, const void*, void*, float, const float*, const float*, int, void*) = nullptr;
+    int (*status)() = nullptr;
+};
+inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
+    static GemmLib g;
+    static std::once_flag once;
+    static std::string err;
+    std::call_once(once, [] {
+        g.lib = dlopen(resolveLib("libfp8gemm.so").c_str(), RTLD_LAZY | RTLD_GLOBAL);
+        if (!g.lib) { err = std::string("fp8gemm: dlopen: ") + dlerror(); return; }
+        g.gemm = sym<decltype(g.gemm)>(g.lib, "fp8_gemm");
+        g.original = sym<decltype(g.original)>(g.lib, "fp8_gemm_original");
+        g.ss = sym<decltype(g.ss)>(g.lib, "fp8_gemm_singlesync");
+        g.scaled = sym<decltype(g.scaled)>(g.lib, "fp8_gemm_scaled");
+        g.status = sym<decltype(g.status)>(g.lib, "fp8_gemm_device_status");
+    });
+    if (!g.lib) throw Error(err);
+    return g;
+}
+inline void* vp(uintptr_t p) { return reinterpret_cast<void*>(p); }
+}  // namespace detail
+
+// C[M,N] (fp16) = A[M,K] x B[N,K]^T on e4m3 device buffers (fp8_gemm.go:52-62).
+inline void FP8GEMM(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr_t C, int mode, uintptr_t stream) {
+    const int rc = detail::gemm_lib().gemm(M, N, K, detail::vp(A), detail::vp(B), detail::vp(C), mode, detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm: CUDA error " + std::to_string(rc));
+}
+// C = alpha * (*scaleA) * (*scaleB) * A x B^T; scale pointers are device addresses or 0.
+inline void FP8GEMMScaled(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr_t C, float alpha, uintptr_t scaleA,
+                          uintptr_t scaleB, int outDType, uintptr_t stream) {
+    const int rc = detail::gemm_lib().scaled(M, N, K, detail::vp(A), detail::vp(B), detail::vp(C), alpha,
+                                             reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
+                                             outDType, detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm_scaled: CUDA error " + std::to_string(rc));
+}
+inline int FP8GEMMDeviceStatus() { return detail::gemm_lib().status(); }
+
+// ----------------------------------------------------------------------------------- attention
+using FAStatus = fa_status_t;
+
+namespace detail {
+struct FaLib {
+    void* lib = nullptr;
+    decltype(&fa_create) create = nullptr;
+    decltype(&fa_destroy) destroy = nullptr;
+    decltype(&fa_version) version = nullptr;
+    decltype(&fa_status_str) status_str = nullptr;
+    decltype(&fa_last_cuda_error) last_err = nullptr;
+    decltype(&fa_forward) forward = nullptr;
+    decltype(&fa_forward_train) forward_train = nullptr;
+    decltype(&fa_forward_ex) forward_ex = nullptr;
+    decltype(&fa_dispatch_select) dispatch = nullptr;
+    decltype(&fa_kernel_name) kernel_name = nullptr;
+    decltype(&fa_device_status) device_status = nullptr;
+};
+inline FaLib& fa_lib() {
+    static FaLib f;
+    static std::once_flag once;
+    static std::string err;
+    std::call_once(once, [] {
+        // search order of fa_forward.go:76-98
+        std::vector<std::string> c;
+        if (!env("GOML_FA_LIB").empty()) c.push_back(env("GOML_FA_LIB"));
+        c.push_back(resolveLib("libfa_sm120.so"));
+        c.push_back("libs/fa_sm120/libfa_sm120.so");
+        c.push_back("./libfa_sm120.so");
+        c.push_back("/usr/local/lib/libfa_sm120.so");
+        std::string last;
+        for (const auto& p : c) {
+            if (p.find('/') != std::string::npos && !is_file(p)) continue;
+            f.lib = dlopen(p.c_str(), RTLD_LAZY);
+            if (f.lib) break;
+            last = dlerror();
+        }
+        if (!f.lib) { err = "fa: dlopen libfa_sm120.so failed (" + last + "); set GOML_FA_LIB"; return; }
+        f.create = sym<decltype(f.create)>(f.lib, "fa_create");
+        f.destroy = sym<decltype(f.destroy)>(f.lib, "fa_destroy");
+        f.version = sym<decltype(f.version)>(f.lib, "fa_version");
+        f.status_str = sym<decltype(f.status_str)>(f.lib, "fa_status_str");
+        f.last_err = sym<decltype(f.last_err)>(f.lib, "fa_last_cuda_error");
+        f.forward = sym<decltype(f.forward)>(f.lib, "fa_forward");
+        f.forward_train = sym<decltype(f.forward_train)>(f.lib, "fa_forward_train");
+        f.forward_ex = sym<decltype(f.forward_ex)>(f.lib, "fa_forward_ex");
+        f.dispatch = sym<decltype(f.dispatch)>(f.lib, "fa_dispatch_select");
+        f.kernel_name = sym<decltype(f.kernel_name)>(f.lib, "fa_kernel_name");
+        f.device_status = sym<decltype(f.device_status)>(f.lib, "fa_device_status");
+    });
+    if (!f.lib) throw Error(err);
+    return f;
+}
+}  // namespace detail
+
+inline void FALoad() { detail::fa_lib(); }
+inline std::string FAVersion() { return detail::fa_lib().version(); }
+inline std::string FAStatusString(FAStatus s) { return detail::fa_lib().status_str(s); }
+inline int FADispatchSelect(int bh, int sl, int hd, int causal, int window) { return detail::fa_lib().dispatch(bh, sl, hd, causal, window); }
+
+// Opaque handle; one per GPU (the device current when it was created).
+class FAContext {
+public:
+    // Create an FA context on the current device.  As fa_forward.go:123-142: when the library hands back a
+    // context together with an error, its message is read and the context destroyed.
+    static std::unique_ptr<FAContext> FACreate() {
+        auto& L = detail::fa_lib();
+        fa_ctx_t* p = nullptr;
+        const FAStatus st = L.create(&p);
+        if (st != FA_OK) {
+            std::string msg = "fa_create: " + std::string(L.status_str(st));
+            if (p) { msg += " (" + std::string(L.last_err(p)) + ")"; L.destroy(p); }
+            throw Error(msg);
+        }
+        return std::unique_ptr<FAContext>(new FAContext(p));
+    }
+    ~FAContext() { Destroy(); }
+    void Destroy() { if (ptr_) { detail::fa_lib().destroy(ptr_); ptr_ = nullptr; } }
+
+    // fa_forward.go:161-183.  q,k,v: e4m3 [bh,sl,hd]; o: fp16; lOut: fp32 [bh,sl] or 0.
+    void ForwardTrain(uintptr_t q, uintptr_t k, uintptr_t v, uintptr_t o, uintptr_t lOut, int bh, int sl, int hd, int causal,
+                      int window, float scale, uintptr_t stream) {
+        check("FAContext.ForwardTrain");
+        const FAStatus st = detail::fa_lib().forward_train(ptr_, detail::vp(q), detail::vp(k), detail::vp(v), detail::vp(o),
+                                                           detail::vp(lOut), bh, sl, hd, causal, window, scale,
+                                                           reinterpret_cast<fa_stream_t>(stream));
+        if (st != FA_OK) fail("fa_forward_train", st);
+    }
+    void Forward(uintptr_t q, uintptr_t k, uintptr_t v, uintptr_t o, int bh, int sl, int hd, int causal, int window, float scale,
+                 uintptr_t stream) {
+        check("FAContext.Forward");
+        const FAStatus st = detail::fa_lib().forward(ptr_, detail::vp(q), detail::vp(k), detail::vp(v), detail::vp(o), bh, sl, hd,
+                                                     causal, window, scale, reinterpret_cast<fa_stream_t>(stream));
+        if (st != FA_OK) fail("fa_forward", st);
+    }
+    void ForwardEx(const fa_forward_args_t& a) {
+        check("FAContext.ForwardEx");
+        const FAStatus st = detail::fa_lib().forward_ex(ptr_, &a);
+        if (st != FA_OK) fail("fa_forward_ex", st);
+    }
+    void DeviceStatus() {
+        const FAStatus st = detail::fa_lib().device_status(ptr_);
+        if (st != FA_OK) fail("fa_device_status", st);
+    }
+
+private:
+    explicit FAContext(fa_ctx_t* p) : ptr_(p) {}
+    void check(const char* who) const { if (!ptr_) throw Error(std::string(who) + ": nil ctx"); }
+    void fail(const char* entry, FAStatus st) const {
+        auto& L = detail::fa_lib();
+        throw Error(std::string(entry) + ": " + L.status_str(st) + " (" + L.last_err(ptr_) + ")");
+    }
+    fa_ctx_t* ptr_;
+};
+
+// ----------------------------------------------------------------------------------- quantiser
+namespace detail {
+struct QuantLib {
+    void* lib = nullptr;
+    int (*quant)(const float*, uint8_t*, float*, float*, size_t, int, void*) = nullptr;
+};
+inline QuantLib& quant_lib() {
+    static QuantLib q;
+    static std::once_flag once;
+    static std::string err;
+    std::call_once(once, [] {
+        q.lib = dlopen(resolveLib("libfp8quant.so").c_str(), RTLD_LAZY);
+        if (!q.lib) { err = std::string("fp8quant: dlopen: ") + dlerror(); return; }
+        q.quant = sym<decltype(q.quant)>(q.lib, "fp8_quantize_f32");
+    });
+    if (!q.lib) throw Error(err);
+    return q;
+}
+inline void quantize(uintptr_t src, uintptr_t dst, uintptr_t scale, uintptr_t amax, size_t n, int conv, uintptr_t stream) {
+    const int rc = quant_lib().quant(reinterpret_cast<const float*>(src), reinterpret_cast<uint8_t*>(dst),
+                                     reinterpret_cast<float*>(scale), reinterpret_cast<float*>(amax), n, conv, vp(stream));
+    if (rc != 0) throw Error("fp8_quantize_f32: CUDA error " + std::to_string(rc));
+}
+}  // namespace detail
+// scale = amax/448 (libs1/fp8_quantize_v2.cu:91)
+inline void QuantizeF32ToF8E4M3(uintptr_t src, uintptr_t dst, uintptr_t scale, uintptr_t amax, size_t n, uintptr_t stream = 0) {
+    detail::quantize(src, dst, scale, amax, n, 0, stream);
+}
+// scale = amax: decoded magnitudes <= 1 (battle_a_llm.go:476)
+inline void QuantizeF32ToF8E4M3Unit(uintptr_t src, uintptr_t dst, uintptr_t scale, uintptr_t amax, size_t n, uintptr_t stream = 0) {
+    detail::quantize(src, dst, scale, amax, n, 1, stream);
+}
+
+// --------------------------------------------------------------------------- multi-GPU manager
+// goml's Backend is single-device (backend/cuda/cuda..go:27,67).  The path shards with no exchange step:
+// attention by contiguous batch*head ranges, the GEMM by blocks of 128-row tiles with the weight replicated.
+struct Shard { long long begin, end; };
+
+inline Shard ShardHeads(long long batchHeads, int world, int rank) {
+    if (world <= 0 || rank < 0 || rank >= world) throw Error("ShardHeads: bad rank/world");
+    const long long base = batchHeads / world, rem = batchHeads % world;
+    const long long b = rank * base + std::min<long long>(rank, rem);
+    return {b, b + base + (rank < rem ? 1 : 0)};
+}
+inline Shard ShardRows(long long M, int world, int rank, int tile = 128) {
+    const long long tiles = (M + tile - 1) / tile;
+    const Shard t = ShardHeads(tiles, world, rank);
+    return {std::min(t.begin * tile, M), std::min(t.end * tile, M)};
+}
+
+// One FA context and one stream per visible device, each created with its device current.
+class DeviceManager {
+public:
+    struct Device {
+        int index;
+        cudaStream_t stream;
+        std::unique_ptr<FAContext> fa;
+    };
+    explicit DeviceManager(int maxDevices = 0) {
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) throw Error("DeviceManager: no CUDA device");
+        if (maxDevices > 0 && maxDevices < n) n = maxDevices;
+        int prev = 0;
+        cudaGetDevice(&prev);
+        for (int d = 0; d < n; d++) {
+            if (cudaSetDevice(d) != cudaSuccess) throw Error("DeviceManager: cudaSetDevice failed");
+            Device dev{d, nullptr, nullptr};
+            if (cudaStreamCreateWithFlags(&dev.stream, cudaStreamNonBlocking) != cudaSuccess) throw Error("DeviceManager: stream");
+            dev.fa = FAContext::FACreate();
+            devices_.push_back(std::move(dev));
+        }
+        cudaSetDevice(prev);
+    }
+    ~DeviceManager() {
+        for (auto& d : devices_) {
+            cudaSetDevice(d.index);
+            d.fa.reset();
+            if (d.stream) cudaStreamDestroy(d.stream);
+        }
+    }
+    int Count() const { return (int)devices_.size(); }
+    // Makes device i current on the calling thread (the libraries use the calling thread's device) and returns it.
+    Device& Use(int i) {
+        if (cudaSetDevice(devices_.at(i).index) != cudaSuccess) throw Error("DeviceManager: cudaSetDevice failed");
+        return devices_[i];
+    }
+    void SyncAll() {
+        for (auto& d : devices_) { cudaSetDevice(d.index); cudaStreamSynchronize(d.stream); }
+    }
+
+private:
+    std::vector<Device> devices_;
+};
+
+}  // namespace cuda
+}  // namespace goml
