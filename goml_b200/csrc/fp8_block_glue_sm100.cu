@@ -1,0 +1,478 @@
+// fp8_block_glue_sm100.cu — libfp8block.so: RMSNorm, half-split RoPE + head permute, SwiGLU and the
+// residual add of a Llama-style decoder block, each fused with the per-tensor e4m3 quantiser that
+// feeds the FP8 GEMM / FP8 attention libraries.
+//
+// All of it is HBM-bound row-local work.  Every op runs as two kernels on the caller's stream: pass 1
+// reduces the per-tensor amax of the op's fp32 result (one atomicMax per CTA), pass 2 recomputes the
+// result and writes codes.  Nothing intermediate is stored, so the traffic per op is
+// 2 x (input bytes) + 1 byte per output element; the second read is served from L2 when the tensor fits
+// (126 MB).  128-bit loads and stores throughout, grids sized to a multiple of the SM count.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fp8_block.h"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+// ---------------------------------------------------------------------------------- small helpers
+__device__ __forceinline__ void bf16x8_to_f32(const uint4 v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        f[2 * k] = __uint_as_float(w[k] << 16);
+        f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void f16x8_to_f32(const uint4 v, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float2 t = __half22float2(h[k]);
+        f[2 * k] = t.x;
+        f[2 * k + 1] = t.y;
+    }
+}
+__device__ __forceinline__ float scale_from_amax(float amax) { return (amax > 1e-12f) ? __fdiv_rn(amax, 448.0f) : 1.0f; }
+
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv) {
+    // y * inv (one rounding), clamp, round-to-nearest-even saturating conversion: the quantiser's formula
+    a = fminf(fmaxf(__fmul_rn(a, inv), -448.f), 448.f);
+    b = fminf(fmaxf(__fmul_rn(b, inv), -448.f), 448.f);
+    c = fminf(fmaxf(__fmul_rn(c, inv), -448.f), 448.f);
+    d = fminf(fmaxf(__fmul_rn(d, inv), -448.f), 448.f);
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+__device__ __forceinline__ uint4 quant16(const float* y, float inv) {
+    return make_uint4(quant4(y[0], y[1], y[2], y[3], inv), quant4(y[4], y[5], y[6], y[7], inv),
+                      quant4(y[8], y[9], y[10], y[11], inv), quant4(y[12], y[13], y[14], y[15], inv));
+}
+__device__ __forceinline__ float absmax16(const float* y, float m) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) m = fmaxf(m, fabsf(y[i]));  // NaN never wins
+    return m;
+}
+
+__device__ __forceinline__ float block_max(float m, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();  // sh may still be read from a previous call
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = sh[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; w++) m = fmaxf(m, sh[w]);
+    return m;
+}
+__device__ __forceinline__ float block_sum(float s, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    s = sh[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; w++) s += sh[w];  // fixed order: the same in every CTA
+    return s;
+}
+// non-negative floats order like their bit patterns
+__device__ __forceinline__ void atomic_amax(float* amax, float m) { atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m)); }
+
+int grid_for(size_t items) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t blocks = (items + THREADS - 1) / THREADS;
+    const size_t cap = (size_t)sms * 8;  // 8 resident CTAs of 256 threads per SM
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+
+// ---------------------------------------------------------------------------------- RoPE table
+__global__ void rope_table_kernel(float* cos_out, float* sin_out, int seq_len, int half, double theta, double hd) {
+    const int n = seq_len * half;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+        const int s = idx / half, i = idx % half;
+        const double ang = (double)s * pow(theta, -2.0 * (double)i / hd);
+        double sv, cv;
+        sincos(ang, &sv, &cv);
+        cos_out[idx] = (float)cv;
+        sin_out[idx] = (float)sv;
+    }
+}
+
+// ---------------------------------------------------------------------------------- RMSNorm (+ residual) + quantise
+// h = x (+ residual) for 4 consecutive elements
+__device__ __forceinline__ float4 load_h4(const float* x, const uint16_t* res, size_t off) {
+    float4 h = *reinterpret_cast<const float4*>(x + off);
+    if (res) {
+        const uint2 r = *reinterpret_cast<const uint2*>(res + off);
+        h.x += __uint_as_float(r.x << 16);
+        h.y += __uint_as_float(r.x & 0xffff0000u);
+        h.z += __uint_as_float(r.y << 16);
+        h.w += __uint_as_float(r.y & 0xffff0000u);
+    }
+    return h;
+}
+
+// pass 1: one CTA per row (grid-stride): h_out, rstd per row, amax of h * rstd * gamma
+__global__ void __launch_bounds__(THREADS) rms_stats_kernel(const float* __restrict__ x, const uint16_t* __restrict__ res,
+                                                            float* h_out, const float* __restrict__ gamma,
+                                                            float* __restrict__ rstd_ws, float* amax, int rows, int hidden,
+                                                            float eps) {
+    __shared__ float sh[THREADS / 32];
+    float run_max = 0.f;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const size_t base = (size_t)row * hidden;
+        float ss = 0.f;
+        for (int c = threadIdx.x * 4; c < hidden; c += THREADS * 4) {
+            const float4 h = load_h4(x, res, base + c);
+            if (res && h_out) *reinterpret_cast<float4*>(h_out + base + c) = h;
+            ss = fmaf(h.x, h.x, ss);
+            ss = fmaf(h.y, h.y, ss);
+            ss = fmaf(h.z, h.z, ss);
+            ss = fmaf(h.w, h.w, ss);
+        }
+        ss = block_sum(ss, sh);
+        const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));
+        if (threadIdx.x == 0) rstd_ws[row] = rstd;
+        // the same thread re-reads what it wrote (or the unchanged inputs)
+        const bool from_h = res && h_out;
+        for (int c = threadIdx.x * 4; c < hidden; c += THREADS * 4) {
+            const float4 h = from_h ? *reinterpret_cast<const float4*>(h_out + base + c) : load_h4(x, res, base + c);
+            const float4 g = *reinterpret_cast<const float4*>(gamma + c);
+            run_max = fmaxf(run_max, fmaxf(fmaxf(fabsf(__fmul_rn(__fmul_rn(h.x, rstd), g.x)), fabsf(__fmul_rn(__fmul_rn(h.y, rstd), g.y))),
+                                           fmaxf(fabsf(__fmul_rn(__fmul_rn(h.z, rstd), g.z)), fabsf(__fmul_rn(__fmul_rn(h.w, rstd), g.w)))));
+        }
+    }
+    run_max = block_max(run_max, sh);
+    if (threadIdx.x == 0) atomic_amax(amax, run_max);
+}
+
+// pass 2: 16 elements per thread per step
+__global__ void __launch_bounds__(THREADS) rms_quant_kernel(const float* __restrict__ h_src, const uint16_t* __restrict__ res,
+                                                            const float* __restrict__ gamma, const float* __restrict__ rstd_ws,
+                                                            const float* __restrict__ amax_ptr, float* scale_out,
+                                                            uint8_t* __restrict__ q, int rows, int hidden) {
+    const float scale = scale_from_amax(*amax_ptr);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const int per_row = hidden / 16;
+    const size_t items = (size_t)rows * per_row;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(it / per_row);
+        const int c = (int)(it % per_row) * 16;
+        const size_t off = (size_t)row * hidden + c;
+        const float rstd = rstd_ws[row];
+        float y[16];
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const float4 h = load_h4(h_src, res, off + 4 * v);
+            const float4 g = *reinterpret_cast<const float4*>(gamma + c + 4 * v);
+            y[4 * v + 0] = __fmul_rn(__fmul_rn(h.x, rstd), g.x);
+            y[4 * v + 1] = __fmul_rn(__fmul_rn(h.y, rstd), g.y);
+            y[4 * v + 2] = __fmul_rn(__fmul_rn(h.z, rstd), g.z);
+            y[4 * v + 3] = __fmul_rn(__fmul_rn(h.w, rstd), g.w);
+        }
+        *reinterpret_cast<uint4*>(q + off) = quant16(y, inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------- RoPE + permute + quantise of Q, K, V
+// One item = 32 elements of one (token, tensor, head): for Q and K the 16 rotation pairs
+// (i, i + hd/2), i in [16c, 16c+16); for V the elements [32c, 32c+32).
+struct QkvItem {
+    int which, b, s, h, c;
+};
+__device__ __forceinline__ QkvItem decode_qkv(size_t it, int seq_len, int heads, int cph) {
+    QkvItem r;
+    r.c = (int)(it % cph);
+    it /= cph;
+    r.h = (int)(it % heads);
+    it /= heads;
+    r.which = (int)(it % 3);
+    it /= 3;
+    r.s = (int)(it % seq_len);
+    r.b = (int)(it / seq_len);
+    return r;
+}
+// y[0..15] = first-half results (or V elements 0..15), y[16..31] = second-half results (or V 16..31)
+__device__ __forceinline__ void qkv_values(const uint16_t* __restrict__ qkv, const float* __restrict__ cos_tab,
+                                           const float* __restrict__ sin_tab, const QkvItem& t, int seq_len, int heads, int hd,
+                                           float* y) {
+    const int half = hd / 2;
+    const size_t row = ((size_t)t.b * seq_len + t.s) * 3 * heads * hd + ((size_t)t.which * heads + t.h) * hd;
+    if (t.which == 2) {
+        const uint4* src = reinterpret_cast<const uint4*>(qkv + row + 32 * t.c);
+#pragma unroll
+        for (int v = 0; v < 4; v++) bf16x8_to_f32(__ldg(src + v), y + 8 * v);
+        return;
+    }
+    float x0[16], x1[16];
+    const uint4* s0 = reinterpret_cast<const uint4*>(qkv + row + 16 * t.c);
+    const uint4* s1 = reinterpret_cast<const uint4*>(qkv + row + half + 16 * t.c);
+    bf16x8_to_f32(__ldg(s0), x0);
+    bf16x8_to_f32(__ldg(s0 + 1), x0 + 8);
+    bf16x8_to_f32(__ldg(s1), x1);
+    bf16x8_to_f32(__ldg(s1 + 1), x1 + 8);
+    const float4* ct = reinterpret_cast<const float4*>(cos_tab + (size_t)t.s * half + 16 * t.c);
+    const float4* st = reinterpret_cast<const float4*>(sin_tab + (size_t)t.s * half + 16 * t.c);
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        const float4 c4 = __ldg(ct + v), s4 = __ldg(st + v);
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int i = 4 * v + e;
+            // x0 c - x1 s ; x0 s + x1 c  (each product rounded, then one add: no contraction)
+            y[i] = __fsub_rn(__fmul_rn(x0[i], cc[e]), __fmul_rn(x1[i], ss[e]));
+            y[16 + i] = __fadd_rn(__fmul_rn(x0[i], ss[e]), __fmul_rn(x1[i], cc[e]));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) qkv_amax_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ cos_tab,
+                                                           const float* __restrict__ sin_tab, float* amaxes, size_t items,
+                                                           int seq_len, int heads, int hd) {
+    __shared__ float sh[THREADS / 32];
+    float m[3] = {0.f, 0.f, 0.f};
+    const int cph = hd / 32;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
+        const QkvItem t = decode_qkv(it, seq_len, heads, cph);
+        float y[32];
+        qkv_values(qkv, cos_tab, sin_tab, t, seq_len, heads, hd, y);
+        const float a = absmax16(y + 16, absmax16(y, 0.f));
+        if (t.which == 0) m[0] = fmaxf(m[0], a);
+        else if (t.which == 1) m[1] = fmaxf(m[1], a);
+        else m[2] = fmaxf(m[2], a);
+    }
+#pragma unroll
+    for (int w = 0; w < 3; w++) {
+        const float r = block_max(m[w], sh);
+        if (threadIdx.x == 0) atomic_amax(amaxes + w, r);
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) qkv_quant_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ cos_tab,
+                                                            const float* __restrict__ sin_tab, const float* __restrict__ amaxes,
+                                                            float* scales, uint8_t* __restrict__ q_out, uint8_t* __restrict__ k_out,
+                                                            uint8_t* __restrict__ v_out, size_t items, int seq_len, int heads, int hd) {
+    float inv[3];
+#pragma unroll
+    for (int w = 0; w < 3; w++) {
+        const float sc = scale_from_amax(amaxes[w]);
+        inv[w] = __fdiv_rn(1.0f, sc);
+        if (blockIdx.x == 0 && threadIdx.x == 0) scales[w] = sc;
+    }
+    const int cph = hd / 32;
+    const int half = hd / 2;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
+        const QkvItem t = decode_qkv(it, seq_len, heads, cph);
+        float y[32];
+        qkv_values(qkv, cos_tab, sin_tab, t, seq_len, heads, hd, y);
+        uint8_t* dst = (t.which == 0 ? q_out : t.which == 1 ? k_out : v_out) + (((size_t)t.b * heads + t.h) * seq_len + t.s) * hd;
+        const float iv = t.which == 0 ? inv[0] : t.which == 1 ? inv[1] : inv[2];
+        if (t.which == 2) {
+            *reinterpret_cast<uint4*>(dst + 32 * t.c) = quant16(y, iv);
+            *reinterpret_cast<uint4*>(dst + 32 * t.c + 16) = quant16(y + 16, iv);
+        } else {
+            *reinterpret_cast<uint4*>(dst + 16 * t.c) = quant16(y, iv);
+            *reinterpret_cast<uint4*>(dst + half + 16 * t.c) = quant16(y + 16, iv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- attention output: permute + quantise
+// item = 16 consecutive elements of one (token, head); out index order so that stores are contiguous
+__device__ __forceinline__ size_t o_src_offset(size_t it, int seq_len, int heads, int hd, size_t* dst_off) {
+    const int cph = hd / 16;
+    const int c = (int)(it % cph);
+    size_t r = it / cph;
+    const int h = (int)(r % heads);
+    r /= heads;
+    const int s = (int)(r % seq_len);
+    const int b = (int)(r / seq_len);
+    *dst_off = (((size_t)b * seq_len + s) * heads + h) * hd + 16 * c;
+    return (((size_t)b * heads + h) * seq_len + s) * hd + 16 * c;
+}
+__global__ void __launch_bounds__(THREADS) o_amax_kernel(const uint16_t* __restrict__ o, float* amax, size_t n16) {
+    __shared__ float sh[THREADS / 32];
+    float m = 0.f;
+    const uint4* src = reinterpret_cast<const uint4*>(o);
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < n16; it += (size_t)gridDim.x * blockDim.x) {
+        float y[16];
+        f16x8_to_f32(__ldg(src + 2 * it), y);
+        f16x8_to_f32(__ldg(src + 2 * it + 1), y + 8);
+        m = absmax16(y, m);
+    }
+    m = block_max(m, sh);
+    if (threadIdx.x == 0) atomic_amax(amax, m);
+}
+__global__ void __launch_bounds__(THREADS) o_quant_kernel(const uint16_t* __restrict__ o, const float* __restrict__ amax_ptr,
+                                                          float* scale_out, uint8_t* __restrict__ q, size_t n16, int seq_len,
+                                                          int heads, int hd) {
+    const float scale = scale_from_amax(*amax_ptr);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < n16; it += (size_t)gridDim.x * blockDim.x) {
+        size_t dst;
+        const size_t src = o_src_offset(it, seq_len, heads, hd, &dst);
+        const uint4* sp = reinterpret_cast<const uint4*>(o + src);
+        float y[16];
+        f16x8_to_f32(__ldg(sp), y);
+        f16x8_to_f32(__ldg(sp + 1), y + 8);
+        *reinterpret_cast<uint4*>(q + dst) = quant16(y, inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------- SwiGLU + quantise
+__device__ __forceinline__ void swiglu16(const uint16_t* __restrict__ gu, size_t row_off, int F, int c, float* y) {
+    const uint4* gp = reinterpret_cast<const uint4*>(gu + row_off + c);
+    const uint4* up = reinterpret_cast<const uint4*>(gu + row_off + F + c);
+    float g[16], u[16];
+    bf16x8_to_f32(__ldg(gp), g);
+    bf16x8_to_f32(__ldg(gp + 1), g + 8);
+    bf16x8_to_f32(__ldg(up), u);
+    bf16x8_to_f32(__ldg(up + 1), u + 8);
+#pragma unroll
+    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(__fdiv_rn(g[i], __fadd_rn(1.0f, expf(-g[i]))), u[i]);  // g / (1 + e^-g) * u
+}
+__global__ void __launch_bounds__(THREADS) swiglu_amax_kernel(const uint16_t* __restrict__ gu, float* amax, int rows, int F) {
+    __shared__ float sh[THREADS / 32];
+    float m = 0.f;
+    const int per_row = F / 16;
+    const size_t items = (size_t)rows * per_row;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
+        float y[16];
+        swiglu16(gu, (it / per_row) * 2 * (size_t)F, F, (int)(it % per_row) * 16, y);
+        m = absmax16(y, m);
+    }
+    m = block_max(m, sh);
+    if (threadIdx.x == 0) atomic_amax(amax, m);
+}
+__global__ void __launch_bounds__(THREADS) swiglu_quant_kernel(const uint16_t* __restrict__ gu, const float* __restrict__ amax_ptr,
+                                                               float* scale_out, uint8_t* __restrict__ q, int rows, int F) {
+    const float scale = scale_from_amax(*amax_ptr);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const int per_row = F / 16;
+    const size_t items = (size_t)rows * per_row;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = it / per_row;
+        const int c = (int)(it % per_row) * 16;
+        float y[16];
+        swiglu16(gu, row * 2 * (size_t)F, F, c, y);
+        *reinterpret_cast<uint4*>(q + row * (size_t)F + c) = quant16(y, inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------- residual add
+__global__ void __launch_bounds__(THREADS) residual_add_kernel(float* __restrict__ x, const uint16_t* __restrict__ y, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        float f[8];
+        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(y) + i), f);
+        float4* xp = reinterpret_cast<float4*>(x) + 2 * i;
+        float4 a = xp[0], b = xp[1];
+        a.x += f[0]; a.y += f[1]; a.z += f[2]; a.w += f[3];
+        b.x += f[4]; b.y += f[5]; b.z += f[6]; b.w += f[7];
+        xp[0] = a;
+        xp[1] = b;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fp8_rope_table(float* cos_out, float* sin_out, int seq_len, int head_dim, float theta, void* stream) {
+    if (!cos_out || !sin_out || seq_len <= 0 || head_dim <= 0 || (head_dim & 1) || !(theta > 0.f)) return (int)cudaErrorInvalidValue;
+    const int half = head_dim / 2;
+    rope_table_kernel<<<grid_for((size_t)seq_len * half), THREADS, 0, (cudaStream_t)stream>>>(cos_out, sin_out, seq_len, half,
+                                                                                             (double)theta, (double)head_dim);
+    return (int)cudaGetLastError();
+}
+
+int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out, const float* gamma, uint8_t* q,
+                         float* scale_out, float* amax_out, float* rstd_ws, int rows, int hidden, float eps, void* stream) {
+    if (!x || !gamma || !q || !scale_out || !amax_out || !rstd_ws) return (int)cudaErrorInvalidValue;
+    if (rows < 0 || hidden <= 0 || (hidden % 16) != 0) return (int)cudaErrorInvalidValue;
+    if (misaligned(x) || misaligned(residual_bf16) || misaligned(h_out) || misaligned(gamma) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const uint16_t* res = reinterpret_cast<const uint16_t*>(residual_bf16);
+    if (rows > 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int grid = rows < sms * 8 ? rows : sms * 8;
+        rms_stats_kernel<<<grid, THREADS, 0, s>>>(x, res, h_out, gamma, rstd_ws, amax_out, rows, hidden, eps);
+    }
+    // pass 2 reads the updated stream where pass 1 stored it
+    const bool from_h = res && h_out;
+    rms_quant_kernel<<<grid_for((size_t)rows * (hidden / 16)), THREADS, 0, s>>>(from_h ? h_out : x, from_h ? nullptr : res, gamma, rstd_ws,
+                                                                               amax_out, scale_out, q, rows, hidden);
+    return (int)cudaGetLastError();
+}
+
+int fp8_rope_quantize_qkv(const void* qkv_bf16, const float* cos_tab, const float* sin_tab, uint8_t* q_out, uint8_t* k_out,
+                          uint8_t* v_out, float* scales, float* amaxes, int batch, int seq_len, int heads, int head_dim,
+                          void* stream) {
+    if (!qkv_bf16 || !cos_tab || !sin_tab || !q_out || !k_out || !v_out || !scales || !amaxes) return (int)cudaErrorInvalidValue;
+    if (batch < 0 || seq_len <= 0 || heads <= 0 || (head_dim != 64 && head_dim != 128)) return (int)cudaErrorInvalidValue;
+    if (misaligned(qkv_bf16) || misaligned(cos_tab) || misaligned(sin_tab) || misaligned(q_out) || misaligned(k_out) || misaligned(v_out))
+        return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(amaxes, 0, 3 * sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const size_t items = (size_t)batch * seq_len * 3 * heads * (head_dim / 32);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(qkv_bf16);
+    if (items > 0) qkv_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, items, seq_len, heads, head_dim);
+    qkv_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, scales, q_out, k_out, v_out, items, seq_len, heads,
+                                                         head_dim);
+    return (int)cudaGetLastError();
+}
+
+int fp8_permute_quantize_heads(const void* o_fp16, uint8_t* q, float* scale_out, float* amax_out, int batch, int seq_len,
+                               int heads, int head_dim, void* stream) {
+    if (!o_fp16 || !q || !scale_out || !amax_out) return (int)cudaErrorInvalidValue;
+    if (batch < 0 || seq_len <= 0 || heads <= 0 || head_dim <= 0 || (head_dim % 16) != 0) return (int)cudaErrorInvalidValue;
+    if (misaligned(o_fp16) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const size_t n16 = (size_t)batch * seq_len * heads * (head_dim / 16);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(o_fp16);
+    if (n16 > 0) o_amax_kernel<<<grid_for(n16), THREADS, 0, s>>>(src, amax_out, n16);
+    o_quant_kernel<<<grid_for(n16), THREADS, 0, s>>>(src, amax_out, scale_out, q, n16, seq_len, heads, head_dim);
+    return (int)cudaGetLastError();
+}
+
+int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, float* amax_out, int rows, int ffn_hidden,
+                        void* stream) {
+    if (!gate_up_bf16 || !q || !scale_out || !amax_out) return (int)cudaErrorInvalidValue;
+    if (rows < 0 || ffn_hidden <= 0 || (ffn_hidden % 16) != 0) return (int)cudaErrorInvalidValue;
+    if (misaligned(gate_up_bf16) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(gate_up_bf16);
+    const size_t items = (size_t)rows * (ffn_hidden / 16);
+    if (items > 0) swiglu_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, rows, ffn_hidden);
+    swiglu_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, scale_out, q, rows, ffn_hidden);
+    return (int)cudaGetLastError();
+}
+
+int fp8_residual_add(float* x, const void* y_bf16, size_t n, void* stream) {
+    if (!x || !y_bf16 || (n % 8) != 0 || misaligned(x) || misaligned(y_bf16)) return (int)cudaErrorInvalidValue;
+    if (n == 0) return 0;
+    residual_add_kernel<<<grid_for(n / 8), THREADS, 0, (cudaStream_t)stream>>>(x, reinterpret_cast<const uint16_t*>(y_bf16), n / 8);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

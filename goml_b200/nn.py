@@ -5,10 +5,12 @@ goml's `nn.Linear.Forward` (nn/linear.go:53-74), `nn.FeedForward.forwardSwiGLU`
 (nn/attention.go:60-160) run in F32 today.  Here every projection goes through the FP8
 GEMM library, the attention through the FP8 attention library and every quantisation
 through the quantiser library — scales stay on the device between them (no host round
-trip).  The glue that is not on the hot path (RMSNorm with eps inside the square root,
-half-split RoPE, SiLU gate, residual adds, layout permutes: the arithmetic of
-internal/abjexam/llama_hf_f64ref.go:126-178 and battle_a_llm_f64ref.go:182-237) runs as
-plain fp32 torch ops on the same stream.
+trip).  The row-local glue (RMSNorm with eps inside the square root, half-split RoPE, SiLU
+gate, residual adds, layout permutes: the arithmetic of
+internal/abjexam/llama_hf_f64ref.go:126-178 and battle_a_llm_f64ref.go:182-237) runs
+through libfp8block.so, each op fused with the quantiser of the next GEMM / attention
+operand (`fused=True`, the default), or as plain fp32 torch ops followed by separate
+quantiser calls (`fused=False`, kept as the unfused comparison).
 
 torch tensors are used as device buffers; all heavy kernels are reached through the C ABI.
 """
@@ -18,7 +20,7 @@ import math
 
 import torch
 
-from . import fa_forward as F, fp8_gemm as G, quantize as Q
+from . import block_glue as BG, fa_forward as F, fp8_gemm as G, quantize as Q
 
 
 class FP8Tensor:
@@ -53,8 +55,11 @@ class FP8Linear:
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         M = x.numel() // self.in_features
-        xq = quantize(x.reshape(M, self.in_features).float())
-        y = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=x.device)
+        return self.forward_codes(quantize(x.reshape(M, self.in_features).float()), M)
+
+    def forward_codes(self, xq: FP8Tensor, M: int) -> torch.Tensor:
+        """The GEMM alone, on an activation that is already e4m3 codes + device scale."""
+        y = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=xq.codes.device)
         G.FP8GEMMScaled(M, self.out_features, self.in_features, xq.codes.data_ptr(), self.w.codes.data_ptr(), y.data_ptr(),
                         1.0, xq.scale_ptr, self.w.scale_ptr, G.OutBF16, torch.cuda.current_stream().cuda_stream)
         return y
@@ -78,7 +83,9 @@ def rope_half_split(x: torch.Tensor, theta: float) -> torch.Tensor:
 class FP8DecoderBlock:
     """Llama-style block: RMSNorm -> QKV -> RoPE -> causal FP8 attention -> O -> residual -> RMSNorm -> SwiGLU -> residual."""
 
-    def __init__(self, d_model, n_heads, ffn_hidden, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0):
+    def __init__(self, d_model, n_heads, ffn_hidden, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0, fused=True):
+        self.fused = fused
+        self._rope = {}   # seq_len -> (cos, sin) device tables
         self.d, self.H, self.F = d_model, n_heads, ffn_hidden
         self.hd = d_model // n_heads
         assert self.hd in (64, 128)
@@ -99,8 +106,52 @@ class FP8DecoderBlock:
                           1.0 / math.sqrt(hd), 1.0, qq.scale_ptr, kq.scale_ptr, vq.scale_ptr, torch.cuda.current_stream().cuda_stream)
         return o.view(B, H, S, hd).permute(0, 2, 1, 3).reshape(B * S, H * hd)
 
+    def rope_tables(self, S: int, dev) -> tuple[torch.Tensor, torch.Tensor]:
+        if S not in self._rope:
+            cos = torch.empty((S, self.hd // 2), dtype=torch.float32, device=dev)
+            sin = torch.empty_like(cos)
+            BG.RopeTable(cos.data_ptr(), sin.data_ptr(), S, self.hd, self.theta, torch.cuda.current_stream().cuda_stream)
+            self._rope[S] = (cos, sin)
+        return self._rope[S]
+
+    def forward_fused(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """The block with every glue op fused with the quantiser of its consumer: 11 library calls, no torch math."""
+        dev, T, d, H, hd, Fh = x.device, B * S, self.d, self.H, self.hd, self.F
+        sh = torch.cuda.current_stream().cuda_stream
+        u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
+        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        h = x.float().clone()                                   # residual stream, updated in place
+        rstd = torch.empty(T, dtype=torch.float32, device=dev)
+        cos, sin = self.rope_tables(S, dev)
+        # attention half
+        xq = FP8Tensor(u8(T, d), sa())
+        BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm1.data_ptr(), xq.codes.data_ptr(), xq.sa.data_ptr(), xq.sa.data_ptr() + 4,
+                           rstd.data_ptr(), T, d, self.eps, sh)
+        qkv = self.qkv.forward_codes(xq, T)                      # [T, 3, H, hd] bf16
+        qc, kc, vc, s3 = u8(B * H, S, hd), u8(B * H, S, hd), u8(B * H, S, hd), sa(6)   # scales[3], amaxes[3]
+        BG.RopeQuantizeQKV(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                           s3.data_ptr(), s3.data_ptr() + 12, B, S, H, hd, sh)
+        o = torch.empty((B * H, S, hd), dtype=torch.float16, device=dev)
+        self.fa.ForwardEx(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, B * H, S, hd, 1, 0, 1.0 / math.sqrt(hd), 1.0,
+                          s3.data_ptr(), s3.data_ptr() + 4, s3.data_ptr() + 8, sh)
+        oq = FP8Tensor(u8(T, d), sa())
+        BG.PermuteQuantizeHeads(o.data_ptr(), oq.codes.data_ptr(), oq.sa.data_ptr(), oq.sa.data_ptr() + 4, B, S, H, hd, sh)
+        ao = self.o.forward_codes(oq, T)
+        # feed-forward half: h += ao, normalise, quantise in one op
+        xq2 = FP8Tensor(u8(T, d), sa())
+        BG.RMSNormQuantize(h.data_ptr(), ao.data_ptr(), h.data_ptr(), self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),
+                           xq2.sa.data_ptr() + 4, rstd.data_ptr(), T, d, self.eps, sh)
+        gu = self.gate_up.forward_codes(xq2, T)                  # [T, 2F] bf16, gate columns first
+        hq = FP8Tensor(u8(T, Fh), sa())
+        BG.SwiGLUQuantize(gu.data_ptr(), hq.codes.data_ptr(), hq.sa.data_ptr(), hq.sa.data_ptr() + 4, T, Fh, sh)
+        ffn = self.down.forward_codes(hq, T)
+        BG.ResidualAdd(h.data_ptr(), ffn.data_ptr(), T * d, sh)
+        return h
+
     def __call__(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
         """x [B*S, d] fp32 -> [B*S, d] fp32."""
+        if self.fused:
+            return self.forward_fused(x, B, S)
         x = x.float()
         x = x + self.o(self.attention(rms_norm(x, self.norm1, self.eps), B, S)).float()
         gu = self.gate_up(rms_norm(x, self.norm2, self.eps)).float()
@@ -138,6 +189,9 @@ def _main():
         return e0.elapsed_time(e1) / iters
 
     total = timed(lambda: blk(x, B, S))
+    blk.fused = False
+    total_unfused = timed(lambda: blk(x, B, S))
+    blk.fused = True
     M = B * S
     # kernels alone, on pre-quantised operands
     xq = quantize(x)
@@ -159,7 +213,8 @@ def _main():
     fl_att = 2.0 * B * H * S * S * hd
     kern = t_qkv + t_o + t_gu + t_dn + t_att
     print(f"block B={B} S={S} d={d} H={H} F={Fh}: total {total:.3f} ms; FP8 kernels {kern:.3f} ms "
-          f"(qkv {t_qkv:.3f}, o {t_o:.3f}, gate+up {t_gu:.3f}, down {t_dn:.3f}, attention {t_att:.3f}); glue+quantise {total - kern:.3f} ms")
+          f"(qkv {t_qkv:.3f}, o {t_o:.3f}, gate+up {t_gu:.3f}, down {t_dn:.3f}, attention {t_att:.3f}); fused glue+quantise {total - kern:.3f} ms; "
+          f"same block with torch glue and separate quantiser calls {total_unfused:.3f} ms")
     print(f"GEMM {fl_gemm / (t_qkv + t_o + t_gu + t_dn) / 1e9:.0f} TFLOPS over {fl_gemm / 1e12:.2f} TFLOP; "
           f"attention (causal) {fl_att / t_att / 1e9:.0f} TFLOPS; whole block {(fl_gemm + fl_att) / total / 1e9:.0f} TFLOPS")
     blk.close()

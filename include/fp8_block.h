@@ -1,0 +1,86 @@
+/*
+ * fp8_block.h — C ABI of libfp8block.so: the row-local glue of a Llama-style
+ * decoder block fused with the per-tensor e4m3 quantiser that feeds the FP8 GEMM
+ * and FP8 attention libraries, for NVIDIA B200 (sm_100a).
+ *
+ * What each entry point replaces in goml:
+ *   - rmsnorm_forward / swiglu_forward / rope_forward of libtransformer.so
+ *     (libs/transformer_kernels.cu:384-438), each followed at the call site by a
+ *     separate quantiser launch (libs1/fp8_quantize_v2.cu:176-204) and, for the
+ *     attention operands, by host round trips for amax and scale
+ *     (internal/abjexam/battle_a_llm.go:380-494);
+ *   - the [S,H,hd] <-> [H,S,hd] permutes of nn/attention.go:100-150.
+ * The arithmetic is that of the reference's fp64 golden for the block
+ * (internal/abjexam/llama_hf_f64ref.go:126-178, battle_a_llm_f64ref.go:182-194 and
+ * :221-237): RMSNorm with eps inside the square root, half-split RoPE (pairs
+ * (i, i + hd/2), angle = pos * theta^(-2i/hd)), SwiGLU silu(gate) * up — evaluated
+ * in fp32 — followed by the quantiser of fp8_quantize.h with scale = amax / 448:
+ *     amax  = max |y|,  scale = amax > 1e-12 ? amax / 448 : 1,  inv = 1 / scale,
+ *     q     = e4m3_rn_satfinite(clamp(y * inv, -448, 448)).
+ *
+ * Every op is two passes over its input (the per-tensor amax must be known before
+ * the first code is written): pass 1 reduces amax (and the row statistics), pass 2
+ * recomputes the values and writes codes.  Nothing but the codes, one scale and one
+ * amax per tensor (and, where stated, the updated residual stream) is written.
+ *
+ * All pointers are device pointers owned by the caller; calls are asynchronous on
+ * `stream`, allocate nothing and clear the amax words themselves.  Activations that
+ * come out of the FP8 GEMM are bf16, the attention output is fp16, the residual
+ * stream is fp32.  Return value: cudaError_t as int, 0 = success;
+ * cudaErrorInvalidValue for null/misaligned pointers or unsupported sizes.
+ */
+#ifndef GOML_FP8_BLOCK_H_
+#define GOML_FP8_BLOCK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__) || defined(__clang__)
+#define FP8BLOCK_API __attribute__((visibility("default")))
+#else
+#define FP8BLOCK_API
+#endif
+
+/* cos/sin tables for half-split RoPE: cos_out, sin_out [seq_len, head_dim/2] fp32,
+ * angle = pos * theta^(-2i/head_dim) evaluated in fp64 (positions 0..seq_len-1). */
+FP8BLOCK_API int fp8_rope_table(float* cos_out, float* sin_out, int seq_len, int head_dim, float theta, void* stream);
+
+/* h = x (+ residual);  y = h * rsqrt(mean(h^2) + eps) * gamma;  q = quantise(y).
+ *   x [rows, hidden] fp32;  residual [rows, hidden] bf16 or NULL;
+ *   h_out [rows, hidden] fp32 or NULL (may alias x): receives h when residual != NULL;
+ *   gamma [hidden] fp32;  q [rows, hidden] e4m3;  rstd_ws [rows] fp32 scratch.
+ * hidden must be a multiple of 16; all tensors 16-byte aligned. */
+FP8BLOCK_API int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out, const float* gamma,
+                                      uint8_t* q, float* scale_out, float* amax_out, float* rstd_ws, int rows,
+                                      int hidden, float eps, void* stream);
+
+/* qkv [batch*seq_len, 3, heads, head_dim] bf16 (the QKV projection's output rows)
+ *   -> RoPE on Q and K -> q_out, k_out, v_out [batch*heads, seq_len, head_dim] e4m3,
+ * each with its own per-tensor scale: scales[3], amaxes[3] (order Q, K, V).
+ * head_dim 64 or 128. */
+FP8BLOCK_API int fp8_rope_quantize_qkv(const void* qkv_bf16, const float* cos_tab, const float* sin_tab,
+                                       uint8_t* q_out, uint8_t* k_out, uint8_t* v_out, float* scales, float* amaxes,
+                                       int batch, int seq_len, int heads, int head_dim, void* stream);
+
+/* Attention output o [batch*heads, seq_len, head_dim] fp16 -> token-major codes
+ * q [batch*seq_len, heads*head_dim] e4m3 (the O projection's A operand).
+ * head_dim a multiple of 16. */
+FP8BLOCK_API int fp8_permute_quantize_heads(const void* o_fp16, uint8_t* q, float* scale_out, float* amax_out,
+                                            int batch, int seq_len, int heads, int head_dim, void* stream);
+
+/* gate_up [rows, 2*ffn_hidden] bf16 (gate columns first) -> silu(gate) * up ->
+ * q [rows, ffn_hidden] e4m3.  ffn_hidden a multiple of 16. */
+FP8BLOCK_API int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, float* amax_out, int rows,
+                                     int ffn_hidden, void* stream);
+
+/* x[i] += y[i] (x fp32 residual stream, y bf16), n a multiple of 8. */
+FP8BLOCK_API int fp8_residual_add(float* x, const void* y_bf16, size_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

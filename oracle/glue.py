@@ -1,0 +1,67 @@
+"""CPU restatement (numpy) of the decoder block's row-local glue ops fused with the per-tensor e4m3
+quantiser.  TEST INFRASTRUCTURE ONLY.
+
+Arithmetic: internal/abjexam/battle_a_llm_f64ref.go:182-194 (rmsNorm, eps inside the square root),
+:221-237 (half-split RoPE: pairs (i, i+hd/2), angle = pos * theta^(-2i/hd)), llama_hf_f64ref.go:160-178
+(SwiGLU silu(gate) * up), evaluated in fp32 in the operation order the product documents, then the
+quantiser of libs1/fp8_quantize_v2.cu:82-122 (scale = amax/448) through `oracle.quantize_f32`.
+"""
+import numpy as np
+
+import oracle as O
+
+f32 = np.float32
+
+
+def bf16_values(a):
+    """Round to bf16 and return the values as float32 (what a bf16 buffer holds)."""
+    return O.round_bf16(np.asarray(a, np.float64)).astype(f32)
+
+
+def rope_table(seq_len, head_dim, theta):
+    half = head_dim // 2
+    ang = np.arange(seq_len, dtype=np.float64)[:, None] * np.float64(theta) ** (-2.0 * np.arange(half, dtype=np.float64) / head_dim)
+    return np.cos(ang).astype(f32), np.sin(ang).astype(f32)
+
+
+def rmsnorm_quantize(x, residual, gamma, eps):
+    """h = x (+ residual); y = (h * rstd) * gamma in fp32; returns (codes, scale, amax, h, y)."""
+    h = np.asarray(x, f32)
+    if residual is not None:
+        h = h + np.asarray(residual, f32)
+    ms = (h.astype(np.float64) ** 2).sum(-1).astype(f32) / f32(h.shape[-1])          # the product sums in fp32
+    rstd = (1.0 / np.sqrt((ms + f32(eps)).astype(np.float64))).astype(f32)              # correctly rounded 1/sqrt
+    y = (h * rstd[:, None]) * np.asarray(gamma, f32)[None, :]
+    codes, scale, amax = O.quantize_f32(np.ascontiguousarray(y))
+    return codes, scale, amax, h, y
+
+
+def rope_quantize_qkv(qkv, cos, sin, B, S, H, hd):
+    """qkv [B*S, 3, H, hd] float32 values -> (codes, scale) for Q, K, V as [B*H, S, hd]."""
+    t = np.asarray(qkv, f32).reshape(B, S, 3, H, hd).transpose(2, 0, 3, 1, 4)  # [3, B, H, S, hd]
+    half = hd // 2
+    out = []
+    for w in range(3):
+        a = t[w]
+        if w < 2:
+            x0, x1 = a[..., :half], a[..., half:]
+            a = np.concatenate([x0 * cos - x1 * sin, x0 * sin + x1 * cos], axis=-1)  # fp32: each product rounded, one add
+        codes, scale, amax = O.quantize_f32(np.ascontiguousarray(a, f32).reshape(B * H, S, hd))
+        out.append((codes, scale, amax))
+    return out
+
+
+def permute_quantize_heads(o, B, S, H, hd):
+    """o [B*H, S, hd] float32 values of fp16 -> codes [B*S, H*hd]."""
+    a = np.asarray(o, f32).reshape(B, H, S, hd).transpose(0, 2, 1, 3).reshape(B * S, H * hd)
+    return O.quantize_f32(np.ascontiguousarray(a))
+
+
+def swiglu_quantize(gu, F):
+    """gu [rows, 2F] float32 values of bf16, gate columns first -> codes [rows, F]."""
+    gu = np.asarray(gu, f32)
+    g, u = gu[:, :F], gu[:, F:]
+    e = np.exp(-g.astype(np.float64)).astype(f32)       # correctly rounded e^-g
+    y = (g / (f32(1.0) + e)) * u
+    codes, scale, amax = O.quantize_f32(np.ascontiguousarray(y))
+    return codes, scale, amax, y

@@ -14,6 +14,7 @@ HEADERS = {
     "fp8_gemm.h": ("FP8GEMM_API", "libfp8gemm.so"),
     "fa_sm120.h": ("FA_API", "libfa_sm120.so"),
     "fp8_quantize.h": ("FP8QUANT_API", "libfp8quant.so"),
+    "fp8_block.h": ("FP8BLOCK_API", "libfp8block.so"),
 }
 
 

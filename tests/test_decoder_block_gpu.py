@@ -18,8 +18,9 @@ from oracle.decoder_block import decoder_block
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("B,S,d,H,Fh", [(2, 256, 512, 4, 1376), (1, 384, 256, 4, 704)])
-def test_block_matches_cpu_restatement(cuda, built_libs, B, S, d, H, Fh):
+def test_block_matches_cpu_restatement(cuda, built_libs, B, S, d, H, Fh, fused):
     from goml_b200 import nn
     cfg = f"block{B}_{S}_{d}"
     w = {n: O.seeded_normal(n, shp, std=0.02, config=cfg) for n, shp in
@@ -28,7 +29,7 @@ def test_block_matches_cpu_restatement(cuda, built_libs, B, S, d, H, Fh):
     g2 = 1.0 + 0.1 * O.seeded_normal("g2", (d,), config=cfg)
     x = O.seeded_normal("x", (B * S, d), config=cfg)
     t = lambda a: torch.from_numpy(a).cuda()
-    blk = nn.FP8DecoderBlock(d, H, Fh, t(w["wqkv"]), t(w["wo"]), t(w["wgate_up"]), t(w["wdown"]), t(g1.astype(np.float32)), t(g2.astype(np.float32)))
+    blk = nn.FP8DecoderBlock(d, H, Fh, t(w["wqkv"]), t(w["wo"]), t(w["wgate_up"]), t(w["wdown"]), t(g1.astype(np.float32)), t(g2.astype(np.float32)), fused=fused)
     y = blk(t(x), B, S)
     torch.cuda.synchronize()
     blk.fa.DeviceStatus()
