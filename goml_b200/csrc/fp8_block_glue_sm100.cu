@@ -5,8 +5,8 @@
 // All of it is HBM-bound row-local work.  Every op runs as two kernels on the caller's stream: pass 1
 // reduces the per-tensor amax of the op's fp32 result (one atomicMax per CTA), pass 2 recomputes the
 // result and writes codes.  Nothing intermediate is stored, so the traffic per op is
-// 2 x (input bytes) + 1 byte per output element; the second read is served from L2 when the tensor fits
-// (126 MB).  128-bit loads and stores throughout, grids sized to a multiple of the SM count.
+// 2 x (input bytes) + 1 byte per output element.  Pass 2 walks the tensor backwards, so it starts on the part
+// pass 1 touched last and is served from L2 (126 MB) for as much of the tensor as still sits there.  128-bit loads and stores throughout, grids sized to a multiple of the SM count.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -19,6 +19,44 @@ namespace {
 constexpr int THREADS = 256;
 
 // ---------------------------------------------------------------------------------- small helpers
+// Division by a run-time constant as multiply-high + shift (numerators below 2^31): the item -> (row, column)
+// decodes below would otherwise cost more instructions than the arithmetic they feed.
+struct FastDiv {
+    uint32_t d, mul, shr;
+    FastDiv() : d(1), mul(0), shr(0) {}
+    explicit FastDiv(uint32_t div) : d(div), mul(0), shr(0) {
+        if (div > 1) {
+            uint32_t lg = 0;
+            while ((1ull << lg) < div) lg++;
+            const uint32_t p = 31 + lg;
+            mul = (uint32_t)(((1ull << p) + div - 1) / div);
+            shr = p - 32;
+        }
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, mul) >> shr; }
+    __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+        q = div(n);
+        r = n - q * d;
+    }
+};
+// 256-bit global loads (sm_100): one instruction per 16 bf16 / 8 fp32 values, 32-byte aligned addresses
+struct U8 {
+    uint32_t v[8];
+};
+__device__ __forceinline__ U8 ldg256(const void* p) {
+    U8 r;
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void bf16x16_to_f32(const U8& r, float* f) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        f[2 * k] = __uint_as_float(r.v[k] << 16);
+        f[2 * k + 1] = __uint_as_float(r.v[k] & 0xffff0000u);
+    }
+}
 __device__ __forceinline__ void bf16x8_to_f32(const uint4 v, float* f) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -93,6 +131,7 @@ int grid_for(size_t items) {
     return (int)blocks;
 }
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; }
+bool misaligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) != 0; }  // operands of 256-bit loads
 
 // ---------------------------------------------------------------------------------- RoPE table
 __global__ void rope_table_kernel(float* cos_out, float* sin_out, int seq_len, int half, double theta, double hd) {
@@ -159,28 +198,47 @@ __global__ void __launch_bounds__(THREADS) rms_stats_kernel(const float* __restr
 __global__ void __launch_bounds__(THREADS) rms_quant_kernel(const float* __restrict__ h_src, const uint16_t* __restrict__ res,
                                                             const float* __restrict__ gamma, const float* __restrict__ rstd_ws,
                                                             const float* __restrict__ amax_ptr, float* scale_out,
-                                                            uint8_t* __restrict__ q, int rows, int hidden) {
+                                                            uint8_t* __restrict__ q, uint32_t items, int hidden,
+                                                            const FastDiv per_row) {
     const float scale = scale_from_amax(*amax_ptr);
     const float inv = __fdiv_rn(1.0f, scale);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    const int per_row = hidden / 16;
-    const size_t items = (size_t)rows * per_row;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
-        const int row = (int)(it / per_row);
-        const int c = (int)(it % per_row) * 16;
-        const size_t off = (size_t)row * hidden + c;
-        const float rstd = rstd_ws[row];
-        float y[16];
+    // two items per step, all loads issued before the first use: twice the bytes in flight per thread
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < items; it += 2 * stride) {
+        uint32_t row[2], c[2];
+        bool live[2];
+        U8 hv[2][2], gv[2][2];
+        float rstd[2];
 #pragma unroll
-        for (int v = 0; v < 4; v++) {
-            const float4 h = load_h4(h_src, res, off + 4 * v);
-            const float4 g = *reinterpret_cast<const float4*>(gamma + c + 4 * v);
-            y[4 * v + 0] = __fmul_rn(__fmul_rn(h.x, rstd), g.x);
-            y[4 * v + 1] = __fmul_rn(__fmul_rn(h.y, rstd), g.y);
-            y[4 * v + 2] = __fmul_rn(__fmul_rn(h.z, rstd), g.z);
-            y[4 * v + 3] = __fmul_rn(__fmul_rn(h.w, rstd), g.w);
+        for (int u = 0; u < 2; u++) {
+            const uint32_t i = it + u * stride;
+            live[u] = i < items;
+            per_row.divmod(items - 1 - (live[u] ? i : it), row[u], c[u]);  // backwards: the rows pass 1 finished with are still in L2
+            c[u] *= 16;
+            const size_t off = (size_t)row[u] * hidden + c[u];
+            hv[u][0] = ldg256(h_src + off);
+            hv[u][1] = ldg256(h_src + off + 8);
+            gv[u][0] = ldg256(gamma + c[u]);
+            gv[u][1] = ldg256(gamma + c[u] + 8);
+            rstd[u] = rstd_ws[row[u]];
         }
-        *reinterpret_cast<uint4*>(q + off) = quant16(y, inv);
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            if (!live[u]) continue;
+            const size_t off = (size_t)row[u] * hidden + c[u];
+            float y[16];
+#pragma unroll
+            for (int v = 0; v < 16; v++) {
+                float h = __uint_as_float(hv[u][v >> 3].v[v & 7]);
+                if (res) {
+                    const uint16_t r = res[off + v];
+                    h += __uint_as_float((uint32_t)r << 16);
+                }
+                y[v] = __fmul_rn(__fmul_rn(h, rstd[u]), __uint_as_float(gv[u][v >> 3].v[v & 7]));
+            }
+            *reinterpret_cast<uint4*>(q + off) = quant16(y, inv);
+        }
     }
 }
 
@@ -190,16 +248,21 @@ __global__ void __launch_bounds__(THREADS) rms_quant_kernel(const float* __restr
 struct QkvItem {
     int which, b, s, h, c;
 };
-__device__ __forceinline__ QkvItem decode_qkv(size_t it, int seq_len, int heads, int cph) {
+struct QkvDivs {
+    FastDiv cph, heads, three, seq;
+};
+__device__ __forceinline__ QkvItem decode_qkv(uint32_t it, const QkvDivs& dv) {
     QkvItem r;
-    r.c = (int)(it % cph);
-    it /= cph;
-    r.h = (int)(it % heads);
-    it /= heads;
-    r.which = (int)(it % 3);
-    it /= 3;
-    r.s = (int)(it % seq_len);
-    r.b = (int)(it / seq_len);
+    uint32_t q, m;
+    dv.cph.divmod(it, q, m);
+    r.c = (int)m;
+    dv.heads.divmod(q, q, m);
+    r.h = (int)m;
+    dv.three.divmod(q, q, m);
+    r.which = (int)m;
+    dv.seq.divmod(q, q, m);
+    r.s = (int)m;
+    r.b = (int)q;
     return r;
 }
 // y[0..15] = first-half results (or V elements 0..15), y[16..31] = second-half results (or V 16..31)
@@ -238,13 +301,12 @@ __device__ __forceinline__ void qkv_values(const uint16_t* __restrict__ qkv, con
 }
 
 __global__ void __launch_bounds__(THREADS) qkv_amax_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ cos_tab,
-                                                           const float* __restrict__ sin_tab, float* amaxes, size_t items,
-                                                           int seq_len, int heads, int hd) {
+                                                           const float* __restrict__ sin_tab, float* amaxes, uint32_t items,
+                                                           int seq_len, int heads, int hd, const QkvDivs dv) {
     __shared__ float sh[THREADS / 32];
     float m[3] = {0.f, 0.f, 0.f};
-    const int cph = hd / 32;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
-        const QkvItem t = decode_qkv(it, seq_len, heads, cph);
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < items; it += gridDim.x * blockDim.x) {
+        const QkvItem t = decode_qkv(it, dv);
         float y[32];
         qkv_values(qkv, cos_tab, sin_tab, t, seq_len, heads, hd, y);
         const float a = absmax16(y + 16, absmax16(y, 0.f));
@@ -262,7 +324,8 @@ __global__ void __launch_bounds__(THREADS) qkv_amax_kernel(const uint16_t* __res
 __global__ void __launch_bounds__(THREADS) qkv_quant_kernel(const uint16_t* __restrict__ qkv, const float* __restrict__ cos_tab,
                                                             const float* __restrict__ sin_tab, const float* __restrict__ amaxes,
                                                             float* scales, uint8_t* __restrict__ q_out, uint8_t* __restrict__ k_out,
-                                                            uint8_t* __restrict__ v_out, size_t items, int seq_len, int heads, int hd) {
+                                                            uint8_t* __restrict__ v_out, uint32_t items, int seq_len, int heads, int hd,
+                                                            const QkvDivs dv) {
     float inv[3];
 #pragma unroll
     for (int w = 0; w < 3; w++) {
@@ -270,10 +333,9 @@ __global__ void __launch_bounds__(THREADS) qkv_quant_kernel(const uint16_t* __re
         inv[w] = __fdiv_rn(1.0f, sc);
         if (blockIdx.x == 0 && threadIdx.x == 0) scales[w] = sc;
     }
-    const int cph = hd / 32;
     const int half = hd / 2;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
-        const QkvItem t = decode_qkv(it, seq_len, heads, cph);
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < items; it += gridDim.x * blockDim.x) {
+        const QkvItem t = decode_qkv(items - 1 - it, dv);  // backwards: see the file header
         float y[32];
         qkv_values(qkv, cos_tab, sin_tab, t, seq_len, heads, hd, y);
         uint8_t* dst = (t.which == 0 ? q_out : t.which == 1 ? k_out : v_out) + (((size_t)t.b * heads + t.h) * seq_len + t.s) * hd;
@@ -290,16 +352,15 @@ __global__ void __launch_bounds__(THREADS) qkv_quant_kernel(const uint16_t* __re
 
 // ---------------------------------------------------------------------------------- attention output: permute + quantise
 // item = 16 consecutive elements of one (token, head); out index order so that stores are contiguous
-__device__ __forceinline__ size_t o_src_offset(size_t it, int seq_len, int heads, int hd, size_t* dst_off) {
-    const int cph = hd / 16;
-    const int c = (int)(it % cph);
-    size_t r = it / cph;
-    const int h = (int)(r % heads);
-    r /= heads;
-    const int s = (int)(r % seq_len);
-    const int b = (int)(r / seq_len);
-    *dst_off = (((size_t)b * seq_len + s) * heads + h) * hd + 16 * c;
-    return (((size_t)b * heads + h) * seq_len + s) * hd + 16 * c;
+struct ODivs {
+    FastDiv cph, heads, seq;
+};
+__device__ __forceinline__ size_t o_src_offset(uint32_t it, int seq_len, int heads, int hd, const ODivs& dv) {
+    uint32_t q, c, h, s;
+    dv.cph.divmod(it, q, c);
+    dv.heads.divmod(q, q, h);
+    dv.seq.divmod(q, q, s);  // q = batch index
+    return (((size_t)q * heads + h) * seq_len + s) * hd + 16 * c;
 }
 __global__ void __launch_bounds__(THREADS) o_amax_kernel(const uint16_t* __restrict__ o, float* amax, size_t n16) {
     __shared__ float sh[THREADS / 32];
@@ -315,60 +376,86 @@ __global__ void __launch_bounds__(THREADS) o_amax_kernel(const uint16_t* __restr
     if (threadIdx.x == 0) atomic_amax(amax, m);
 }
 __global__ void __launch_bounds__(THREADS) o_quant_kernel(const uint16_t* __restrict__ o, const float* __restrict__ amax_ptr,
-                                                          float* scale_out, uint8_t* __restrict__ q, size_t n16, int seq_len,
-                                                          int heads, int hd) {
+                                                          float* scale_out, uint8_t* __restrict__ q, uint32_t n16, int seq_len,
+                                                          int heads, int hd, const ODivs dv) {
     const float scale = scale_from_amax(*amax_ptr);
     const float inv = __fdiv_rn(1.0f, scale);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < n16; it += (size_t)gridDim.x * blockDim.x) {
-        size_t dst;
-        const size_t src = o_src_offset(it, seq_len, heads, hd, &dst);
-        const uint4* sp = reinterpret_cast<const uint4*>(o + src);
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < n16; it += gridDim.x * blockDim.x) {
+        const uint32_t rit = n16 - 1 - it;   // destination order (token-major), walked backwards
+        const uint4* sp = reinterpret_cast<const uint4*>(o + o_src_offset(rit, seq_len, heads, hd, dv));
         float y[16];
         f16x8_to_f32(__ldg(sp), y);
         f16x8_to_f32(__ldg(sp + 1), y + 8);
-        *reinterpret_cast<uint4*>(q + dst) = quant16(y, inv);
+        *reinterpret_cast<uint4*>(q + (size_t)rit * 16) = quant16(y, inv);
     }
 }
 
 // ---------------------------------------------------------------------------------- SwiGLU + quantise
-__device__ __forceinline__ void swiglu16(const uint16_t* __restrict__ gu, size_t row_off, int F, int c, float* y) {
-    const uint4* gp = reinterpret_cast<const uint4*>(gu + row_off + c);
-    const uint4* up = reinterpret_cast<const uint4*>(gu + row_off + F + c);
+__device__ __forceinline__ void swiglu16(const U8& gv, const U8& uv, float* y) {
     float g[16], u[16];
-    bf16x8_to_f32(__ldg(gp), g);
-    bf16x8_to_f32(__ldg(gp + 1), g + 8);
-    bf16x8_to_f32(__ldg(up), u);
-    bf16x8_to_f32(__ldg(up + 1), u + 8);
+    bf16x16_to_f32(gv, g);
+    bf16x16_to_f32(uv, u);
 #pragma unroll
-    for (int i = 0; i < 16; i++) y[i] = __fmul_rn(__fdiv_rn(g[i], __fadd_rn(1.0f, expf(-g[i]))), u[i]);  // g / (1 + e^-g) * u
+    for (int i = 0; i < 16; i++)  // g / (1 + e^-g) * u with the hardware exponential and reciprocal (a few fp32 ulp)
+        y[i] = __fmul_rn(__fmul_rn(g[i], __frcp_rn(__fadd_rn(1.0f, __expf(-g[i])))), u[i]);
 }
-__global__ void __launch_bounds__(THREADS) swiglu_amax_kernel(const uint16_t* __restrict__ gu, float* amax, int rows, int F) {
+__global__ void __launch_bounds__(THREADS) swiglu_amax_kernel(const uint16_t* __restrict__ gu, float* amax, uint32_t items, int F,
+                                                              const FastDiv per_row) {
     __shared__ float sh[THREADS / 32];
     float m = 0.f;
-    const int per_row = F / 16;
-    const size_t items = (size_t)rows * per_row;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
-        float y[16];
-        swiglu16(gu, (it / per_row) * 2 * (size_t)F, F, (int)(it % per_row) * 16, y);
-        m = absmax16(y, m);
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < items; it += 2 * stride) {  // two items per step, loads first
+        U8 gv[2], uv[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t i = it + u * stride;
+            live[u] = i < items;
+            uint32_t row, c;
+            per_row.divmod(live[u] ? i : it, row, c);
+            const uint16_t* gp = gu + (size_t)row * 2 * F + c * 16;
+            gv[u] = ldg256(gp);
+            uv[u] = ldg256(gp + F);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            float y[16];
+            swiglu16(gv[u], uv[u], y);
+            if (live[u]) m = absmax16(y, m);
+        }
     }
     m = block_max(m, sh);
     if (threadIdx.x == 0) atomic_amax(amax, m);
 }
 __global__ void __launch_bounds__(THREADS) swiglu_quant_kernel(const uint16_t* __restrict__ gu, const float* __restrict__ amax_ptr,
-                                                               float* scale_out, uint8_t* __restrict__ q, int rows, int F) {
+                                                               float* scale_out, uint8_t* __restrict__ q, uint32_t items, int F,
+                                                               const FastDiv per_row) {
     const float scale = scale_from_amax(*amax_ptr);
     const float inv = __fdiv_rn(1.0f, scale);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
-    const int per_row = F / 16;
-    const size_t items = (size_t)rows * per_row;
-    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = it / per_row;
-        const int c = (int)(it % per_row) * 16;
-        float y[16];
-        swiglu16(gu, row * 2 * (size_t)F, F, c, y);
-        *reinterpret_cast<uint4*>(q + row * (size_t)F + c) = quant16(y, inv);
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < items; it += 2 * stride) {  // two items per step, loads first
+        U8 gv[2], uv[2];
+        bool live[2];
+        size_t dst[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const uint32_t i = it + u * stride;
+            live[u] = i < items;
+            uint32_t row, c;
+            per_row.divmod(items - 1 - (live[u] ? i : it), row, c);  // backwards: see the file header
+            const uint16_t* gp = gu + (size_t)row * 2 * F + c * 16;
+            gv[u] = ldg256(gp);
+            uv[u] = ldg256(gp + F);
+            dst[u] = (size_t)row * F + c * 16;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            float y[16];
+            swiglu16(gv[u], uv[u], y);
+            if (live[u]) *reinterpret_cast<uint4*>(q + dst[u]) = quant16(y, inv);
+        }
     }
 }
 
@@ -402,7 +489,7 @@ int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out
                          float* scale_out, float* amax_out, float* rstd_ws, int rows, int hidden, float eps, void* stream) {
     if (!x || !gamma || !q || !scale_out || !amax_out || !rstd_ws) return (int)cudaErrorInvalidValue;
     if (rows < 0 || hidden <= 0 || (hidden % 16) != 0) return (int)cudaErrorInvalidValue;
-    if (misaligned(x) || misaligned(residual_bf16) || misaligned(h_out) || misaligned(gamma) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    if (misaligned32(x) || misaligned(residual_bf16) || misaligned32(h_out) || misaligned32(gamma) || misaligned(q)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
@@ -415,8 +502,10 @@ int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out
     }
     // pass 2 reads the updated stream where pass 1 stored it
     const bool from_h = res && h_out;
-    rms_quant_kernel<<<grid_for((size_t)rows * (hidden / 16)), THREADS, 0, s>>>(from_h ? h_out : x, from_h ? nullptr : res, gamma, rstd_ws,
-                                                                               amax_out, scale_out, q, rows, hidden);
+    const size_t items = (size_t)rows * (hidden / 16);
+    if (items >= (1ull << 31)) return (int)cudaErrorInvalidValue;
+    rms_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(from_h ? h_out : x, from_h ? nullptr : res, gamma, rstd_ws, amax_out, scale_out, q,
+                                                         (uint32_t)items, hidden, FastDiv(hidden / 16));
     return (int)cudaGetLastError();
 }
 
@@ -431,10 +520,17 @@ int fp8_rope_quantize_qkv(const void* qkv_bf16, const float* cos_tab, const floa
     cudaError_t e = cudaMemsetAsync(amaxes, 0, 3 * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
     const size_t items = (size_t)batch * seq_len * 3 * heads * (head_dim / 32);
+    if (items >= (1ull << 31)) return (int)cudaErrorInvalidValue;
     const uint16_t* src = reinterpret_cast<const uint16_t*>(qkv_bf16);
-    if (items > 0) qkv_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, items, seq_len, heads, head_dim);
-    qkv_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, scales, q_out, k_out, v_out, items, seq_len, heads,
-                                                         head_dim);
+    QkvDivs dv;
+    dv.cph = FastDiv(head_dim / 32);
+    dv.heads = FastDiv(heads);
+    dv.three = FastDiv(3);
+    dv.seq = FastDiv(seq_len);
+    if (items > 0)
+        qkv_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, (uint32_t)items, seq_len, heads, head_dim, dv);
+    qkv_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, scales, q_out, k_out, v_out, (uint32_t)items, seq_len,
+                                                         heads, head_dim, dv);
     return (int)cudaGetLastError();
 }
 
@@ -447,9 +543,14 @@ int fp8_permute_quantize_heads(const void* o_fp16, uint8_t* q, float* scale_out,
     cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
     const size_t n16 = (size_t)batch * seq_len * heads * (head_dim / 16);
+    if (n16 >= (1ull << 31)) return (int)cudaErrorInvalidValue;
     const uint16_t* src = reinterpret_cast<const uint16_t*>(o_fp16);
+    ODivs dv;
+    dv.cph = FastDiv(head_dim / 16);
+    dv.heads = FastDiv(heads);
+    dv.seq = FastDiv(seq_len);
     if (n16 > 0) o_amax_kernel<<<grid_for(n16), THREADS, 0, s>>>(src, amax_out, n16);
-    o_quant_kernel<<<grid_for(n16), THREADS, 0, s>>>(src, amax_out, scale_out, q, n16, seq_len, heads, head_dim);
+    o_quant_kernel<<<grid_for(n16), THREADS, 0, s>>>(src, amax_out, scale_out, q, (uint32_t)n16, seq_len, heads, head_dim, dv);
     return (int)cudaGetLastError();
 }
 
@@ -457,14 +558,16 @@ int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, 
                         void* stream) {
     if (!gate_up_bf16 || !q || !scale_out || !amax_out) return (int)cudaErrorInvalidValue;
     if (rows < 0 || ffn_hidden <= 0 || (ffn_hidden % 16) != 0) return (int)cudaErrorInvalidValue;
-    if (misaligned(gate_up_bf16) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    if (misaligned32(gate_up_bf16) || misaligned(q)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
     const uint16_t* src = reinterpret_cast<const uint16_t*>(gate_up_bf16);
     const size_t items = (size_t)rows * (ffn_hidden / 16);
-    if (items > 0) swiglu_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, rows, ffn_hidden);
-    swiglu_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, scale_out, q, rows, ffn_hidden);
+    if (items >= (1ull << 31)) return (int)cudaErrorInvalidValue;
+    const FastDiv per_row(ffn_hidden / 16);
+    if (items > 0) swiglu_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, (uint32_t)items, ffn_hidden, per_row);
+    swiglu_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, scale_out, q, (uint32_t)items, ffn_hidden, per_row);
     return (int)cudaGetLastError();
 }
 

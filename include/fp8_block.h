@@ -53,7 +53,7 @@ FP8BLOCK_API int fp8_rope_table(float* cos_out, float* sin_out, int seq_len, int
  *   x [rows, hidden] fp32;  residual [rows, hidden] bf16 or NULL;
  *   h_out [rows, hidden] fp32 or NULL (may alias x): receives h when residual != NULL;
  *   gamma [hidden] fp32;  q [rows, hidden] e4m3;  rstd_ws [rows] fp32 scratch.
- * hidden must be a multiple of 16; all tensors 16-byte aligned. */
+ * hidden must be a multiple of 16; x, h_out and gamma 32-byte aligned, the others 16-byte. */
 FP8BLOCK_API int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out, const float* gamma,
                                       uint8_t* q, float* scale_out, float* amax_out, float* rstd_ws, int rows,
                                       int hidden, float eps, void* stream);
@@ -73,7 +73,7 @@ FP8BLOCK_API int fp8_permute_quantize_heads(const void* o_fp16, uint8_t* q, floa
                                             int batch, int seq_len, int heads, int head_dim, void* stream);
 
 /* gate_up [rows, 2*ffn_hidden] bf16 (gate columns first) -> silu(gate) * up ->
- * q [rows, ffn_hidden] e4m3.  ffn_hidden a multiple of 16. */
+ * q [rows, ffn_hidden] e4m3.  ffn_hidden a multiple of 16; gate_up 32-byte aligned. */
 FP8BLOCK_API int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, float* amax_out, int rows,
                                      int ffn_hidden, void* stream);
 
