@@ -50,6 +50,15 @@ __device__ __forceinline__ U8 ldg256(const void* p) {
                  : "l"(p));
     return r;
 }
+// same through the coherent path: for buffers the kernel also writes (the residual stream updated in place)
+__device__ __forceinline__ U8 ld256(const void* p) {
+    U8 r;
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+                 : "l"(p)
+                 : "memory");
+    return r;
+}
 __device__ __forceinline__ void bf16x16_to_f32(const U8& r, float* f) {
 #pragma unroll
     for (int k = 0; k < 8; k++) {
@@ -160,37 +169,120 @@ __device__ __forceinline__ float4 load_h4(const float* x, const uint16_t* res, s
     return h;
 }
 
-// pass 1: one CTA per row (grid-stride): h_out, rstd per row, amax of h * rstd * gamma
+// The normalised value is evaluated as y = (h * gamma) * rstd, each product rounded to fp32.  Multiplying by the
+// positive row constant rstd is monotonic even after rounding, so max_i |y_i| of a row is exactly
+// fl(max_i |fl(h_i * gamma_i)| * rstd): pass 1 needs ONE sweep over the row (sum of squares and that maximum
+// together) and one block-wide reduction, instead of a second sweep that waits for rstd.
+__device__ __forceinline__ void block_sum_max(float& s, float& m, float* sh) {  // sh[2 * THREADS / 32]
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    }
+    __syncthreads();  // sh may still be read from the previous row
+    if ((threadIdx.x & 31) == 0) {
+        sh[threadIdx.x >> 5] = s;
+        sh[THREADS / 32 + (threadIdx.x >> 5)] = m;
+    }
+    __syncthreads();
+    s = sh[0];
+    m = sh[THREADS / 32];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; w++) {  // fixed order: the same in every CTA
+        s += sh[w];
+        m = fmaxf(m, sh[THREADS / 32 + w]);
+    }
+}
+
+// pass 1, any hidden (multiple of 16): one CTA per row (grid-stride): h_out, rstd per row, amax
 __global__ void __launch_bounds__(THREADS) rms_stats_kernel(const float* __restrict__ x, const uint16_t* __restrict__ res,
                                                             float* h_out, const float* __restrict__ gamma,
                                                             float* __restrict__ rstd_ws, float* amax, int rows, int hidden,
                                                             float eps) {
-    __shared__ float sh[THREADS / 32];
+    __shared__ float sh[2 * THREADS / 32];
     float run_max = 0.f;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const size_t base = (size_t)row * hidden;
-        float ss = 0.f;
+        float ss = 0.f, m1 = 0.f;
         for (int c = threadIdx.x * 4; c < hidden; c += THREADS * 4) {
             const float4 h = load_h4(x, res, base + c);
             if (res && h_out) *reinterpret_cast<float4*>(h_out + base + c) = h;
+            const float4 g = *reinterpret_cast<const float4*>(gamma + c);
             ss = fmaf(h.x, h.x, ss);
             ss = fmaf(h.y, h.y, ss);
             ss = fmaf(h.z, h.z, ss);
             ss = fmaf(h.w, h.w, ss);
+            m1 = fmaxf(fmaxf(m1, fmaxf(fabsf(__fmul_rn(h.x, g.x)), fabsf(__fmul_rn(h.y, g.y)))),
+                       fmaxf(fabsf(__fmul_rn(h.z, g.z)), fabsf(__fmul_rn(h.w, g.w))));
         }
-        ss = block_sum(ss, sh);
+        block_sum_max(ss, m1, sh);
         const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));
         if (threadIdx.x == 0) rstd_ws[row] = rstd;
-        // the same thread re-reads what it wrote (or the unchanged inputs)
-        const bool from_h = res && h_out;
-        for (int c = threadIdx.x * 4; c < hidden; c += THREADS * 4) {
-            const float4 h = from_h ? *reinterpret_cast<const float4*>(h_out + base + c) : load_h4(x, res, base + c);
-            const float4 g = *reinterpret_cast<const float4*>(gamma + c);
-            run_max = fmaxf(run_max, fmaxf(fmaxf(fabsf(__fmul_rn(__fmul_rn(h.x, rstd), g.x)), fabsf(__fmul_rn(__fmul_rn(h.y, rstd), g.y))),
-                                           fmaxf(fabsf(__fmul_rn(__fmul_rn(h.z, rstd), g.z)), fabsf(__fmul_rn(__fmul_rn(h.w, rstd), g.w)))));
-        }
+        run_max = fmaxf(run_max, __fmul_rn(m1, rstd));
     }
-    run_max = block_max(run_max, sh);
+    if (threadIdx.x == 0) atomic_amax(amax, run_max);
+}
+
+// pass 1 for hidden = N * 2048 (N = 1, 2, 4): the row lives in registers (N 256-bit loads per thread) and the
+// next row's loads are issued before this row's reductions, so the two block-wide reductions per row no longer
+// drain the memory pipeline.
+__device__ __forceinline__ void st256(void* p, const U8& r) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]),
+                 "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7])
+                 : "memory");
+}
+template <int N, bool HAS_RES>
+struct RowRegs {
+    U8 x[N];
+    uint4 r[HAS_RES ? N : 1];
+};
+template <int N, bool HAS_RES>
+__device__ __forceinline__ void load_row(RowRegs<N, HAS_RES>& t, const float* x, const uint16_t* res, size_t base) {
+#pragma unroll
+    for (int k = 0; k < N; k++) {
+        const size_t off = base + (size_t)k * (THREADS * 8) + threadIdx.x * 8;
+        t.x[k] = ld256(x + off);
+        if (HAS_RES) t.r[k] = __ldg(reinterpret_cast<const uint4*>(res + off));
+    }
+}
+template <int N, bool HAS_RES>
+__global__ void __launch_bounds__(THREADS) rms_stats_regs_kernel(const float* __restrict__ x, const uint16_t* __restrict__ res, float* h_out,
+                                                                 const float* __restrict__ gamma, float* __restrict__ rstd_ws, float* amax,
+                                                                 int rows, float eps) {
+    constexpr int hidden = N * THREADS * 8;
+    __shared__ float sh[2 * THREADS / 32];
+    float run_max = 0.f;
+    U8 g[N];
+#pragma unroll
+    for (int k = 0; k < N; k++) g[k] = ldg256(gamma + k * (THREADS * 8) + threadIdx.x * 8);
+    RowRegs<N, HAS_RES> cur, nxt;
+    int row = blockIdx.x;
+    if (row < rows) load_row<N, HAS_RES>(cur, x, res, (size_t)row * hidden);
+    for (; row < rows; row += gridDim.x) {
+        const int next = row + gridDim.x;
+        if (next < rows) load_row<N, HAS_RES>(nxt, x, res, (size_t)next * hidden);
+        float ss = 0.f, m1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < N; k++) {
+            float rf[8];
+            if (HAS_RES) bf16x8_to_f32(cur.r[k], rf);
+            U8 o;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float h = __uint_as_float(cur.x[k].v[i]);
+                if (HAS_RES) h += rf[i];
+                o.v[i] = __float_as_uint(h);
+                ss = fmaf(h, h, ss);
+                m1 = fmaxf(m1, fabsf(__fmul_rn(h, __uint_as_float(g[k].v[i]))));
+            }
+            if (HAS_RES && h_out) st256(h_out + (size_t)row * hidden + (size_t)k * (THREADS * 8) + threadIdx.x * 8, o);
+        }
+        block_sum_max(ss, m1, sh);
+        const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));
+        if (threadIdx.x == 0) rstd_ws[row] = rstd;
+        run_max = fmaxf(run_max, __fmul_rn(m1, rstd));
+        if (next < rows) cur = nxt;
+    }
     if (threadIdx.x == 0) atomic_amax(amax, run_max);
 }
 
@@ -235,7 +327,7 @@ __global__ void __launch_bounds__(THREADS) rms_quant_kernel(const float* __restr
                     const uint16_t r = res[off + v];
                     h += __uint_as_float((uint32_t)r << 16);
                 }
-                y[v] = __fmul_rn(__fmul_rn(h, rstd[u]), __uint_as_float(gv[u][v >> 3].v[v & 7]));
+                y[v] = __fmul_rn(__fmul_rn(h, __uint_as_float(gv[u][v >> 3].v[v & 7])), rstd[u]);
             }
             *reinterpret_cast<uint4*>(q + off) = quant16(y, inv);
         }
@@ -392,13 +484,18 @@ __global__ void __launch_bounds__(THREADS) o_quant_kernel(const uint16_t* __rest
 }
 
 // ---------------------------------------------------------------------------------- SwiGLU + quantise
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void swiglu16(const U8& gv, const U8& uv, float* y) {
     float g[16], u[16];
     bf16x16_to_f32(gv, g);
     bf16x16_to_f32(uv, u);
 #pragma unroll
     for (int i = 0; i < 16; i++)  // g / (1 + e^-g) * u with the hardware exponential and reciprocal (a few fp32 ulp)
-        y[i] = __fmul_rn(__fmul_rn(g[i], __frcp_rn(__fadd_rn(1.0f, __expf(-g[i])))), u[i]);
+        y[i] = __fmul_rn(__fmul_rn(g[i], rcp_approx(__fadd_rn(1.0f, __expf(-g[i])))), u[i]);
 }
 __global__ void __launch_bounds__(THREADS) swiglu_amax_kernel(const uint16_t* __restrict__ gu, float* amax, uint32_t items, int F,
                                                               const FastDiv per_row) {
@@ -498,7 +595,14 @@ int fp8_rmsnorm_quantize(const float* x, const void* residual_bf16, float* h_out
         int dev = 0, sms = 148;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const int grid = rows < sms * 8 ? rows : sms * 8;
-        rms_stats_kernel<<<grid, THREADS, 0, s>>>(x, res, h_out, gamma, rstd_ws, amax_out, rows, hidden, eps);
+#define RMS_STATS_REGS(N)                                                                                               \
+    (res ? rms_stats_regs_kernel<N, true><<<grid, THREADS, 0, s>>>(x, res, h_out, gamma, rstd_ws, amax_out, rows, eps) \
+         : rms_stats_regs_kernel<N, false><<<grid, THREADS, 0, s>>>(x, res, h_out, gamma, rstd_ws, amax_out, rows, eps))
+        if (hidden == 2048) RMS_STATS_REGS(1);
+        else if (hidden == 4096) RMS_STATS_REGS(2);
+        else if (hidden == 8192) RMS_STATS_REGS(4);
+        else rms_stats_kernel<<<grid, THREADS, 0, s>>>(x, res, h_out, gamma, rstd_ws, amax_out, rows, hidden, eps);
+#undef RMS_STATS_REGS
     }
     // pass 2 reads the updated stream where pass 1 stored it
     const bool from_h = res && h_out;

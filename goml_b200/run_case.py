@@ -3,6 +3,7 @@
     python -m goml_b200.run_case fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
     python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
+    python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
 
 torch only allocates the device buffers; every launch goes through the C ABI.
 """
@@ -11,7 +12,7 @@ import sys
 
 import torch
 
-from . import fa_forward as F, fp8_gemm as G, quantize as Q
+from . import block_glue as BG, fa_forward as F, fp8_gemm as G, quantize as Q
 
 
 def main(argv):
@@ -44,6 +45,43 @@ def main(argv):
         for _ in range(iters):
             Q.QuantizeF32ToF8E4M3(x.data_ptr(), q.data_ptr(), s.data_ptr(), s.data_ptr() + 4, n, 0)
         torch.cuda.synchronize()
+    elif kind == "glue":
+        B, S, d, H, Fh, iters = args
+        T, hd, dev = B * S, d // H, "cuda"
+        x = torch.randn(T, d, device=dev)
+        res = torch.randn(T, d, device=dev).bfloat16()
+        gamma = torch.ones(d, device=dev)
+        q = torch.empty(T, d, dtype=torch.uint8, device=dev)
+        sa = torch.zeros(8, device=dev)
+        rstd = torch.empty(T, device=dev)
+        qkv = torch.randn(T, 3 * d, device=dev).bfloat16()
+        cos = torch.empty(S, hd // 2, device=dev)
+        sin = torch.empty_like(cos)
+        qc, kc, vc = (torch.empty(B * H, S, hd, dtype=torch.uint8, device=dev) for _ in range(3))
+        o = torch.randn(B * H, S, hd, device=dev).half()
+        gu = torch.randn(T, 2 * Fh, device=dev).bfloat16()
+        hq = torch.empty(T, Fh, dtype=torch.uint8, device=dev)
+        BG.RopeTable(cos.data_ptr(), sin.data_ptr(), S, hd, 10000.0)
+        p = lambda t: t.data_ptr()
+        ops = {   # name -> (call, bytes if every input were read once)
+            "rmsnorm_quantize": (lambda: BG.RMSNormQuantize(p(x), 0, 0, p(gamma), p(q), p(sa), p(sa) + 4, p(rstd), T, d, 1e-5), T * d * 5),
+            "rmsnorm_quantize+residual": (lambda: BG.RMSNormQuantize(p(x), p(res), p(x), p(gamma), p(q), p(sa), p(sa) + 4, p(rstd), T, d, 1e-5), T * d * 11),
+            "rope_quantize_qkv": (lambda: BG.RopeQuantizeQKV(p(qkv), p(cos), p(sin), p(qc), p(kc), p(vc), p(sa), p(sa) + 12, B, S, H, hd), T * d * 9),
+            "permute_quantize_heads": (lambda: BG.PermuteQuantizeHeads(p(o), p(q), p(sa), p(sa) + 4, B, S, H, hd), T * d * 3),
+            "swiglu_quantize": (lambda: BG.SwiGLUQuantize(p(gu), p(hq), p(sa), p(sa) + 4, T, Fh), T * Fh * 5),
+            "residual_add": (lambda: BG.ResidualAdd(p(x), p(res), T * d), T * d * 10),
+        }
+        for name, (fn, nbytes) in ops.items():
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / iters * 1e3
+            print(f"{name:28s} {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of single-read bytes")
     else:
         raise SystemExit(__doc__)
     print("ok")

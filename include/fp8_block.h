@@ -49,7 +49,7 @@ extern "C" {
  * angle = pos * theta^(-2i/head_dim) evaluated in fp64 (positions 0..seq_len-1). */
 FP8BLOCK_API int fp8_rope_table(float* cos_out, float* sin_out, int seq_len, int head_dim, float theta, void* stream);
 
-/* h = x (+ residual);  y = h * rsqrt(mean(h^2) + eps) * gamma;  q = quantise(y).
+/* h = x (+ residual);  y = (h * gamma) * rsqrt(mean(h^2) + eps), each product rounded to fp32;  q = quantise(y).
  *   x [rows, hidden] fp32;  residual [rows, hidden] bf16 or NULL;
  *   h_out [rows, hidden] fp32 or NULL (may alias x): receives h when residual != NULL;
  *   gamma [hidden] fp32;  q [rows, hidden] e4m3;  rstd_ws [rows] fp32 scratch.

@@ -25,13 +25,13 @@ def rope_table(seq_len, head_dim, theta):
 
 
 def rmsnorm_quantize(x, residual, gamma, eps):
-    """h = x (+ residual); y = (h * rstd) * gamma in fp32; returns (codes, scale, amax, h, y)."""
+    """h = x (+ residual); y = (h * gamma) * rstd in fp32; returns (codes, scale, amax, h, y)."""
     h = np.asarray(x, f32)
     if residual is not None:
         h = h + np.asarray(residual, f32)
     ms = (h.astype(np.float64) ** 2).sum(-1).astype(f32) / f32(h.shape[-1])          # the product sums in fp32
     rstd = (1.0 / np.sqrt((ms + f32(eps)).astype(np.float64))).astype(f32)              # correctly rounded 1/sqrt
-    y = (h * rstd[:, None]) * np.asarray(gamma, f32)[None, :]
+    y = (h * np.asarray(gamma, f32)[None, :]) * rstd[:, None]
     codes, scale, amax = O.quantize_f32(np.ascontiguousarray(y))
     return codes, scale, amax, h, y
 

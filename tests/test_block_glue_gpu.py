@@ -35,7 +35,7 @@ def nearly_same_codes(got, want, frac=1e-4):
     assert (steps != 0).mean() <= frac, (steps != 0).mean()
 
 
-@pytest.mark.parametrize("rows,hidden,with_res", [(96, 512, False), (300, 4096, True), (7, 1040, True), (0, 64, False)])
+@pytest.mark.parametrize("rows,hidden,with_res", [(96, 512, False), (300, 4096, True), (2500, 4096, False), (64, 2048, False), (40, 8192, True), (7, 1040, True), (0, 64, False)])
 def test_rmsnorm_quantize(cuda, built_libs, rows, hidden, with_res):
     from goml_b200 import block_glue as BG
     cfg = f"rms{rows}_{hidden}"
