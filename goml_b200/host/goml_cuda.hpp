@@ -275,6 +275,75 @@ inline void QuantizeF32ToF8E4M3Unit(uintptr_t src, uintptr_t dst, uintptr_t scal
     detail::quantize(src, dst, scale, amax, n, 1, stream);
 }
 
+// ----------------------------------------------------------------------- decoder-block glue
+// libfp8block.so: RMSNorm (+ residual), half-split RoPE + head permute of Q/K/V, head permute of the attention
+// output, SwiGLU and the residual add, each fused with the quantiser of its consumer.  They take the place of
+// libtransformer.so's rmsnorm_forward / rope_forward / swiglu_forward (libs/transformer_kernels.cu:384-438)
+// followed by separate quantiser launches (internal/abjexam/battle_a_llm.go:380-494).
+namespace detail {
+struct BlockLib {
+    void* lib = nullptr;
+    int (*rope_table)(float*, float*, int, int, float, void*) = nullptr;
+    int (*rmsnorm_q)(const float*, const void*, float*, const float*, uint8_t*, float*, float*, float*, int, int, float, void*) = nullptr;
+    int (*rope_q)(const void*, const float*, const float*, uint8_t*, uint8_t*, uint8_t*, float*, float*, int, int, int, int, void*) = nullptr;
+    int (*permute_q)(const void*, uint8_t*, float*, float*, int, int, int, int, void*) = nullptr;
+    int (*swiglu_q)(const void*, uint8_t*, float*, float*, int, int, void*) = nullptr;
+    int (*residual_add)(float*, const void*, size_t, void*) = nullptr;
+};
+inline BlockLib& block_lib() {
+    static BlockLib b;
+    static std::once_flag once;
+    static std::string err;
+    std::call_once(once, [] {
+        b.lib = dlopen(resolveLib("libfp8block.so").c_str(), RTLD_LAZY);
+        if (!b.lib) { err = std::string("fp8block: dlopen: ") + dlerror(); return; }
+        b.rope_table = sym<decltype(b.rope_table)>(b.lib, "fp8_rope_table");
+        b.rmsnorm_q = sym<decltype(b.rmsnorm_q)>(b.lib, "fp8_rmsnorm_quantize");
+        b.rope_q = sym<decltype(b.rope_q)>(b.lib, "fp8_rope_quantize_qkv");
+        b.permute_q = sym<decltype(b.permute_q)>(b.lib, "fp8_permute_quantize_heads");
+        b.swiglu_q = sym<decltype(b.swiglu_q)>(b.lib, "fp8_swiglu_quantize");
+        b.residual_add = sym<decltype(b.residual_add)>(b.lib, "fp8_residual_add");
+    });
+    if (!b.lib) throw Error(err);
+    return b;
+}
+inline void block_check(const char* what, int rc) {
+    if (rc != 0) throw Error(std::string(what) + ": CUDA error " + std::to_string(rc));
+}
+template <class T>
+inline T* tp(uintptr_t p) { return reinterpret_cast<T*>(p); }
+}  // namespace detail
+inline void RopeTable(uintptr_t cos, uintptr_t sin, int seqLen, int headDim, float theta, uintptr_t stream = 0) {
+    detail::block_check("fp8_rope_table", detail::block_lib().rope_table(detail::tp<float>(cos), detail::tp<float>(sin), seqLen, headDim, theta, detail::vp(stream)));
+}
+// residualBF16 and hOut may be 0; hOut may equal x (the residual stream is then updated in place)
+inline void RMSNormQuantize(uintptr_t x, uintptr_t residualBF16, uintptr_t hOut, uintptr_t gamma, uintptr_t q, uintptr_t scale, uintptr_t amax,
+                            uintptr_t rstdWs, int rows, int hidden, float eps, uintptr_t stream = 0) {
+    detail::block_check("fp8_rmsnorm_quantize",
+                        detail::block_lib().rmsnorm_q(detail::tp<const float>(x), detail::vp(residualBF16), detail::tp<float>(hOut), detail::tp<const float>(gamma),
+                                                      detail::tp<uint8_t>(q), detail::tp<float>(scale), detail::tp<float>(amax), detail::tp<float>(rstdWs), rows,
+                                                      hidden, eps, detail::vp(stream)));
+}
+inline void RopeQuantizeQKV(uintptr_t qkvBF16, uintptr_t cos, uintptr_t sin, uintptr_t q, uintptr_t k, uintptr_t v, uintptr_t scales, uintptr_t amaxes,
+                            int batch, int seqLen, int heads, int headDim, uintptr_t stream = 0) {
+    detail::block_check("fp8_rope_quantize_qkv",
+                        detail::block_lib().rope_q(detail::vp(qkvBF16), detail::tp<const float>(cos), detail::tp<const float>(sin), detail::tp<uint8_t>(q),
+                                                   detail::tp<uint8_t>(k), detail::tp<uint8_t>(v), detail::tp<float>(scales), detail::tp<float>(amaxes), batch,
+                                                   seqLen, heads, headDim, detail::vp(stream)));
+}
+inline void PermuteQuantizeHeads(uintptr_t oFP16, uintptr_t q, uintptr_t scale, uintptr_t amax, int batch, int seqLen, int heads, int headDim,
+                                 uintptr_t stream = 0) {
+    detail::block_check("fp8_permute_quantize_heads", detail::block_lib().permute_q(detail::vp(oFP16), detail::tp<uint8_t>(q), detail::tp<float>(scale),
+                                                                                    detail::tp<float>(amax), batch, seqLen, heads, headDim, detail::vp(stream)));
+}
+inline void SwiGLUQuantize(uintptr_t gateUpBF16, uintptr_t q, uintptr_t scale, uintptr_t amax, int rows, int ffnHidden, uintptr_t stream = 0) {
+    detail::block_check("fp8_swiglu_quantize", detail::block_lib().swiglu_q(detail::vp(gateUpBF16), detail::tp<uint8_t>(q), detail::tp<float>(scale),
+                                                                             detail::tp<float>(amax), rows, ffnHidden, detail::vp(stream)));
+}
+inline void ResidualAdd(uintptr_t x, uintptr_t yBF16, size_t n, uintptr_t stream = 0) {
+    detail::block_check("fp8_residual_add", detail::block_lib().residual_add(detail::tp<float>(x), detail::vp(yBF16), n, detail::vp(stream)));
+}
+
 // --------------------------------------------------------------------------- multi-GPU manager
 // goml's Backend is single-device (backend/cuda/cuda..go:27,67).  The path shards with no exchange step:
 // attention by contiguous batch*head ranges, the GEMM by blocks of 128-row tiles with the weight replicated.

@@ -60,6 +60,9 @@ static int run_cpu(const char* libs_dir) {
         }
     CHECK(ShardRows(16384, 8, 3).begin == 6144 && ShardRows(16384, 8, 3).end == 8192);
     CHECK(ShardRows(300, 2, 1).begin == 256 && ShardRows(300, 2, 1).end == 300);
+    // block glue: argument errors before any launch, same message shape
+    CHECK(thrown([] { SwiGLUQuantize(64, 64, 64, 64, 2, 40, 0); }) == "fp8_swiglu_quantize: CUDA error 1");
+    CHECK(thrown([] { ResidualAdd(64, 64, 12, 0); }) == "fp8_residual_add: CUDA error 1");
     return fails;
 }
 
@@ -218,6 +221,37 @@ static int run_gpu() {
             std::copy(part.begin(), part.end(), sharded.begin() + off);
         }
         CHECK(sharded == hO);
+    }
+    {   // block glue through the host layer: residual add exact, SwiGLU codes decode to silu(g)*u within one e4m3 step
+        const int rows = 8, F = 64;
+        std::vector<float> xs(rows * F);
+        std::vector<uint16_t> yb(rows * F), gu(rows * 2 * F);
+        auto bf16 = [](float f) { uint32_t u; std::memcpy(&u, &f, 4); return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1)) >> 16); };
+        auto bf2f = [](uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; std::memcpy(&f, &u, 4); return f; };
+        for (int i = 0; i < rows * F; i++) { xs[i] = std::sin(0.37f * i); yb[i] = bf16(std::cos(0.11f * i)); }
+        for (int i = 0; i < rows * 2 * F; i++) gu[i] = bf16(3.0f * std::sin(0.05f * i + 1.0f));
+        DevBuf<float> dx(rows * F), sa(2);
+        DevBuf<uint16_t> dy(rows * F), dgu(rows * 2 * F);
+        DevBuf<uint8_t> dq(rows * F);
+        dx.up(xs); dy.up(yb); dgu.up(gu);
+        ResidualAdd(dx.addr(), dy.addr(), (size_t)rows * F, 0);
+        SwiGLUQuantize(dgu.addr(), dq.addr(), sa.addr(), sa.addr() + 4, rows, F, 0);
+        cudaDeviceSynchronize();
+        auto hx = dx.down();
+        auto hq = dq.down();
+        auto hs = sa.down();
+        bool exact = true;
+        double worst = 0, amax = 0;
+        for (int i = 0; i < rows * F; i++) exact = exact && hx[i] == xs[i] + bf2f(yb[i]);
+        for (int r = 0; r < rows; r++)
+            for (int c = 0; c < F; c++) {
+                const double g = bf2f(gu[r * 2 * F + c]), u = bf2f(gu[r * 2 * F + F + c]);
+                const double ref = g / (1.0 + std::exp(-g)) * u;
+                amax = std::max(amax, std::fabs(ref));
+                worst = std::max(worst, std::fabs(e4m3_decode(hq[r * F + c]) * hs[0] - ref) / std::max(std::fabs(ref), 1e-3));
+            }
+        std::printf("glue: residual add exact %d, swiglu worst relative step %.3f, amax %.6f vs %.6f\n", (int)exact, worst, hs[1], amax);
+        CHECK(exact && worst <= 0.07 && std::fabs(hs[1] - amax) <= 1e-5 * amax && std::fabs(hs[0] - hs[1] / 448.0f) <= 1e-7f);
     }
     // argument errors carry the reference's message shape (fa_forward.go:176-181)
     const std::string msg = thrown([&] { ctx.ForwardTrain(0, 16, 16, 16, 0, 1, 64, 128, 0, 0, 1.0f, 0); });
