@@ -47,7 +47,8 @@ def test_rmsnorm_quantize(cuda, built_libs, rows, hidden, with_res):
     q = torch.full((max(rows, 1), hidden), 0xAA, dtype=torch.uint8, device="cuda")
     sa = torch.full((2,), 7.0, dtype=torch.float32, device="cuda")
     rstd = torch.empty(max(rows, 1), dtype=torch.float32, device="cuda")
-    BG.RMSNormQuantize(xd.data_ptr(), rd.data_ptr() if with_res else 0, xd.data_ptr() if with_res else 0, dev(gamma).data_ptr(),
+    gd = dev(gamma)
+    BG.RMSNormQuantize(xd.data_ptr(), rd.data_ptr() if with_res else 0, xd.data_ptr() if with_res else 0, gd.data_ptr(),
                        q.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, rstd.data_ptr(), rows, hidden, 1e-5)
     torch.cuda.synchronize()
     if rows == 0:
@@ -75,7 +76,8 @@ def test_rope_quantize_qkv_bit_exact(cuda, built_libs, B, S, H, hd):
     cos, sin = dev(c_ref), dev(s_ref)
     out = [torch.full((B * H, S, hd), 0xAA, dtype=torch.uint8, device="cuda") for _ in range(3)]
     s6 = torch.full((6,), 9.0, dtype=torch.float32, device="cuda")
-    BG.RopeQuantizeQKV(dev(qkv, torch.bfloat16).data_ptr(), cos.data_ptr(), sin.data_ptr(), out[0].data_ptr(), out[1].data_ptr(),
+    qkv_d = dev(qkv, torch.bfloat16)
+    BG.RopeQuantizeQKV(qkv_d.data_ptr(), cos.data_ptr(), sin.data_ptr(), out[0].data_ptr(), out[1].data_ptr(),
                        out[2].data_ptr(), s6.data_ptr(), s6.data_ptr() + 12, B, S, H, hd)
     torch.cuda.synchronize()
     want = glue.rope_quantize_qkv(qkv, c_ref, s_ref, B, S, H, hd)
@@ -91,7 +93,8 @@ def test_permute_quantize_heads_bit_exact(cuda, built_libs, B, S, H, hd):
     o = O.round_fp16(O.seeded_normal("o", (B * H, S, hd), config=f"perm{B}_{S}_{H}_{hd}")).astype(np.float32)
     q = torch.full((B * S, H * hd), 0xAA, dtype=torch.uint8, device="cuda")
     sa = torch.zeros(2, dtype=torch.float32, device="cuda")
-    BG.PermuteQuantizeHeads(dev(o, torch.float16).data_ptr(), q.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, B, S, H, hd)
+    od = dev(o, torch.float16)
+    BG.PermuteQuantizeHeads(od.data_ptr(), q.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, B, S, H, hd)
     torch.cuda.synchronize()
     codes, scale, amax = glue.permute_quantize_heads(o, B, S, H, hd)
     assert sa.tolist() == [scale, amax]
@@ -104,7 +107,8 @@ def test_swiglu_quantize(cuda, built_libs, rows, F):
     gu = glue.bf16_values(2.0 * O.seeded_normal("gu", (rows, 2 * F), config=f"swiglu{rows}_{F}"))
     q = torch.full((rows, F), 0xAA, dtype=torch.uint8, device="cuda")
     sa = torch.zeros(2, dtype=torch.float32, device="cuda")
-    BG.SwiGLUQuantize(dev(gu, torch.bfloat16).data_ptr(), q.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, rows, F)
+    gud = dev(gu, torch.bfloat16)
+    BG.SwiGLUQuantize(gud.data_ptr(), q.data_ptr(), sa.data_ptr(), sa.data_ptr() + 4, rows, F)
     torch.cuda.synchronize()
     codes, scale, amax, _ = glue.swiglu_quantize(gu, F)
     assert abs(sa[0].item() - scale) <= 1e-6 * scale and abs(sa[1].item() - amax) <= 1e-6 * amax
@@ -116,7 +120,8 @@ def test_residual_add_exact(cuda, built_libs):
     x = O.seeded_normal("x", (1000, 72), config="resadd").astype(np.float32)
     y = glue.bf16_values(O.seeded_normal("y", (1000, 72), config="resadd"))
     xd = dev(x)
-    BG.ResidualAdd(xd.data_ptr(), dev(y, torch.bfloat16).data_ptr(), x.size)
+    yd = dev(y, torch.bfloat16)
+    BG.ResidualAdd(xd.data_ptr(), yd.data_ptr(), x.size)
     torch.cuda.synchronize()
     assert np.array_equal(xd.cpu().numpy(), x + y)
 
