@@ -64,6 +64,8 @@ struct GemmParams {
     const float* scale_b;
     int out_bf16;
     int m_tiles, n_tiles, k_blocks;
+    int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
+    int num_units;   // split_from + 2 * (number of split tiles)
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
@@ -74,6 +76,25 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
     const int r = t - g * per_group;
     tm = first_m + r % gsize;
     tn = r / gsize;
+}
+
+// Work unit u -> tile coordinates, first column and width.  Units below split_from are whole tiles; above it,
+// two consecutive units are the left and right halves of one tile (only instantiated for BN = 256).
+template <int BN>
+__device__ __forceinline__ void unit_coords(int u, const GemmParams& p, int& tm, int& n0, int& bn) {
+    int t = u, half = -1;
+    if (BN == 256 && u >= p.split_from) {
+        t = p.split_from + ((u - p.split_from) >> 1);
+        half = (u - p.split_from) & 1;
+    }
+    int tn;
+    tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+    n0 = tn * BN;
+    bn = BN;
+    if (half >= 0) {
+        bn = BN / 2;
+        n0 += half * (BN / 2);
+    }
 }
 
 __device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
@@ -88,7 +109,7 @@ __device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
     constexpr int STAGES = Tile<BN>::STAGES;
     constexpr int STAGE_BYTES = Tile<BN>::STAGE_BYTES;
     constexpr int TMEM_COLS = Tile<BN>::TMEM_COLS;
@@ -107,7 +128,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int num_units = p.num_units;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -138,16 +159,17 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             int stage = 0;
             uint32_t phase = 1;  // "previous phase complete": the ring starts empty
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int tm, tn;
-                tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                int tm, n0, bn;
+                unit_coords<BN>(u, p, tm, n0, bn);
+                const CUtensorMap* tb = (bn == BN) ? &tmap_b : &tmap_b_half;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
                     const uint32_t sa = smem_base + stage * STAGE_BYTES;
-                    mbar_arrive_expect_tx(fb, STAGE_BYTES);
+                    mbar_arrive_expect_tx(fb, A_BYTES + bn * BK);
                     tma_load_2d(sa, &tmap_a, fb, kb * BK, tm * BM);
-                    tma_load_2d(sa + A_BYTES, &tmap_b, fb, kb * BK, tn * BN);
+                    tma_load_2d(sa + A_BYTES, tb, fb, kb * BK, n0);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -155,13 +177,14 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_e4m3_f32(BM, BN, 0, 0);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t tphase[2] = {1, 1};  // both accumulator buffers start free
             int buf = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const bool whole = !(BN == 256 && u >= p.split_from);
+                const uint32_t idesc = whole ? make_idesc_e4m3_f32(BM, BN, 0, 0) : make_idesc_e4m3_f32(BM, BN / 2, 0, 0);
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_MMA)) break;
                 tphase[buf] ^= 1;
                 tc_fence_after();
@@ -194,9 +217,9 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
         uint32_t tphase[2] = {0, 0};
         int buf = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            int tm, tn;
-            tile_coords(t, p.m_tiles, p.n_tiles, tm, tn);
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+            int tm, n0, bn;
+            unit_coords<BN>(u, p, tm, n0, bn);
             if (!mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_EPILOGUE)) break;
             tphase[buf] ^= 1;
             tc_fence_after();
@@ -204,8 +227,8 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                const int col0 = tn * BN + c * 32;
+            for (int c = 0; c < bn / 32; c++) {
+                const int col0 = n0 + c * 32;
                 if (col0 >= p.N) break;  // uniform across the CTA
                 uint32_t acc[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, acc);
@@ -320,16 +343,25 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
 
-    CUtensorMap ta, tb;
+    // The last wave: when the 128x256 tiling leaves it at most half full, its tiles run as two 128x128 units each
+    // (same MMA efficiency per flop), so that wave takes half the time instead of idling most SMs.
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles >= (1ll << 30)) return (int)cudaErrorInvalidValue;
+    const int rem = (int)(tiles % st.num_sms);
+    const bool split_tail = (bn == 256) && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
+    p.split_from = (int)(split_tail ? tiles - rem : tiles);
+    p.num_units = (int)(split_tail ? tiles + rem : tiles);
+
+    CUtensorMap ta, tb, tbh;
     if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint32_t)bn, BK, CU_TENSOR_MAP_SWIZZLE_128B))
+        !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint32_t)bn, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_tmap_u8_2d(&tbh, B, (uint64_t)N, (uint64_t)K, (uint32_t)(bn == 256 ? 128 : bn), BK, CU_TENSOR_MAP_SWIZZLE_128B))
         return (int)cudaErrorInvalidValue;
 
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    const int grid = (int)(tiles < st.num_sms ? tiles : st.num_sms);
-    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, p);
-    else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, p);
-    else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, p);
+    const int grid = (int)(p.num_units < st.num_sms ? p.num_units : st.num_sms);
+    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
+    else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
+    else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
     return (int)cudaGetLastError();
 }
 

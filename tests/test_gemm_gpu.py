@@ -61,7 +61,9 @@ def test_device_scale_pointers(cuda, built_libs):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 8, 16), (16, 8192, 256), (129, 257, 160), (300, 520, 144), (127, 255, 4096),
-                                    (130, 7, 48), (5, 1000, 16)])
+                                    (130, 7, 48), (5, 1000, 16),
+                                    # 150 / 190 tiles of 128x256 on 148 SMs: the last wave runs as half-width units
+                                    (256, 19200, 160), (640, 9700, 144)])
 def test_ragged_and_tiny_shapes(cuda, built_libs, M, N, K):
     rng = np.random.default_rng(M * 1000 + N)
     a = rng.integers(0, 0x7F, (M, K), dtype=np.uint8) | (rng.integers(0, 2, (M, K), dtype=np.uint8) << 7)
