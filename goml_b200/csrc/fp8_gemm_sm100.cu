@@ -32,6 +32,9 @@ constexpr int BK = 128;          // K bytes per pipeline stage (one 128-byte swi
 constexpr int A_BYTES = BM * BK;
 constexpr int NUM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr int GROUP_M = 16;       // tile-order band height (in tiles)
+// epilogue staging for the fp32 accumulate mode: per epilogue warp two 32-row x 128-byte boxes (128-byte swizzle)
+constexpr int STAGING_BOX = 32 * 128;
+constexpr int STAGING_BYTES = 4 * 2 * STAGING_BOX;
 
 // Tile width BN (columns of C per tile = TMEM columns per accumulator buffer).  256 is the
 // tensor-efficient shape (the MMA reads (128+BN)*32 operand bytes per BN/2 clocks, within the
@@ -44,7 +47,7 @@ struct Tile {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers (a power of two >= 32)
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 enum : uint32_t {
@@ -63,6 +66,8 @@ struct GemmParams {
     const float* scale_a;
     const float* scale_b;
     int out_bf16;
+    float* X;  // when set: X[M,N] (fp32) += alpha * A.B^T instead of storing C (the residual-stream update of a decoder block)
+    int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
     int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
     int num_units;   // split_from + 2 * (number of split tiles)
@@ -109,7 +114,8 @@ __device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
+                        const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_x,
+                        const GemmParams p) {
     constexpr int STAGES = Tile<BN>::STAGES;
     constexpr int STAGE_BYTES = Tile<BN>::STAGE_BYTES;
     constexpr int TMEM_COLS = Tile<BN>::TMEM_COLS;
@@ -117,13 +123,14 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     // operand tiles need 1024-byte alignment (swizzle atom = 8 rows x 128 B)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    const uint32_t staging = smem_base + STAGES * STAGE_BYTES;
+    const uint32_t bars = staging + STAGING_BYTES;
     // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
     const uint32_t bar_full = bars;
     const uint32_t bar_empty = bars + 8 * STAGES;
     const uint32_t bar_tfull = bars + 16 * STAGES;
     const uint32_t bar_tempty = bar_tfull + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 16 * STAGES + 32);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + STAGING_BYTES + 16 * STAGES + 32);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -215,8 +222,10 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (p.scale_a) alpha *= __ldg(p.scale_a);
         if (p.scale_b) alpha *= __ldg(p.scale_b);
         const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+        const bool xvec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.X) & 15) == 0);
         uint32_t tphase[2] = {0, 0};
         int buf = 0;
+        int sbuf = 0;  // staging box in use (accumulate mode)
         for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
             int tm, n0, bn;
             unit_coords<BN>(u, p, tm, n0, bn);
@@ -233,7 +242,45 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 uint32_t acc[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, acc);
                 tmem_ld_wait();
-                if (row < p.M) {
+                if (p.X && p.x_tma) {
+                    // X += tile through the memory system: own row of the 32 x 32 box into swizzled staging, then one
+                    // TMA reduce-add per warp and chunk (rows >= M and columns >= N are clipped by the tensor map)
+                    const uint32_t box = staging + (quad * 2 + sbuf) * STAGING_BOX;
+                    if (lane == 0) tma_store_wait_read<1>();  // the reduce that used this buffer two chunks ago has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int v = 0; v < 8; v++) {
+                        const uint32_t dst = box + lane * 128 + ((v ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(__uint_as_float(acc[4 * v + 0]) * alpha),
+                                     "f"(__uint_as_float(acc[4 * v + 1]) * alpha), "f"(__uint_as_float(acc[4 * v + 2]) * alpha),
+                                     "f"(__uint_as_float(acc[4 * v + 3]) * alpha)
+                                     : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_reduce_add_2d(&tmap_x, box, col0, tm * BM + quad * 32);
+                        tma_store_commit();
+                    }
+                    sbuf ^= 1;
+                } else if (row < p.M && p.X) {
+                    float* xrow = p.X + (size_t)row * p.N + col0;
+                    if (xvec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 8; v++) {
+                            float4 x = *reinterpret_cast<float4*>(xrow + 4 * v);
+                            x.x = fmaf(__uint_as_float(acc[4 * v + 0]), alpha, x.x);
+                            x.y = fmaf(__uint_as_float(acc[4 * v + 1]), alpha, x.y);
+                            x.z = fmaf(__uint_as_float(acc[4 * v + 2]), alpha, x.z);
+                            x.w = fmaf(__uint_as_float(acc[4 * v + 3]), alpha, x.w);
+                            *reinterpret_cast<float4*>(xrow + 4 * v) = x;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < p.N) xrow[j] = fmaf(__uint_as_float(acc[j]), alpha, xrow[j]);
+                    }
+                } else if (row < p.M) {
                     if (vec_ok && col0 + 32 <= p.N) {
                         uint4* dst = reinterpret_cast<uint4*>(crow + col0);
 #pragma unroll
@@ -264,6 +311,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             buf ^= 1;
         }
+        if (p.X && p.x_tma && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
 
     // ------------------------------------------------------------- teardown
@@ -294,13 +342,13 @@ constexpr int MAX_DEVICES = 64;
 DeviceState g_dev[MAX_DEVICES];
 
 int launch(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* sa, const float* sb,
-           int out_bf16, cudaStream_t stream) {
+           int out_bf16, cudaStream_t stream, float* X = nullptr) {
     if (M < 0 || N < 0 || K < 0) return (int)cudaErrorInvalidValue;
     if (M == 0 || N == 0) return 0;
-    if (!A || !B || !C) return (int)cudaErrorInvalidValue;
+    if (!A || !B || (!C && !X)) return (int)cudaErrorInvalidValue;
     if (K == 0 || (K % 16) != 0) return (int)cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
-        (reinterpret_cast<uintptr_t>(C) & 1))
+        (reinterpret_cast<uintptr_t>(C) & 1) || (reinterpret_cast<uintptr_t>(X) & 3))
         return (int)cudaErrorInvalidValue;
 
     int dev = 0;
@@ -339,6 +387,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
+    p.X = X;
+    p.x_tma = (X && (N % 4) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) ? 1 : 0;
     p.m_tiles = (int)m_tiles;
     p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
@@ -358,10 +408,13 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
         !make_tmap_u8_2d(&tbh, B, (uint64_t)N, (uint64_t)K, (uint32_t)(bn == 256 ? 128 : bn), BK, CU_TENSOR_MAP_SWIZZLE_128B))
         return (int)cudaErrorInvalidValue;
 
+    CUtensorMap tx = ta;  // placeholder when there is nothing to describe
+    if (p.x_tma && !make_tmap_f32_2d(&tx, X, (uint64_t)M, (uint64_t)N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
+
     const int grid = (int)(p.num_units < st.num_sms ? p.num_units : st.num_sms);
-    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
-    else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
-    else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, tbh, p);
+    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
+    else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
+    else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
     return (int)cudaGetLastError();
 }
 
@@ -386,6 +439,12 @@ int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* B, void* C, 
                     const float* scale_b, int out_dtype, void* stream) {
     if (out_dtype != FP8_GEMM_OUT_FP16 && out_dtype != FP8_GEMM_OUT_BF16) return (int)cudaErrorInvalidValue;
     return launch(M, N, K, A, B, C, alpha, scale_a, scale_b, out_dtype == FP8_GEMM_OUT_BF16, (cudaStream_t)stream);
+}
+
+int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, const void* B, float* X, float alpha, const float* scale_a,
+                            const float* scale_b, void* stream) {
+    if (!X) return (int)cudaErrorInvalidValue;
+    return launch(M, N, K, A, B, nullptr, alpha, scale_a, scale_b, 0, (cudaStream_t)stream, X);
 }
 
 int fp8_gemm_device_status(void) {

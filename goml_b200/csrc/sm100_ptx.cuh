@@ -120,6 +120,13 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src,
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// 2-D tiled reduce-add shared -> global: global[tile] += shared[tile], performed by the memory system (element type
+// from the tensor map); parts of the box outside the tensor are skipped.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

@@ -42,6 +42,8 @@ def _init():
                     fn.argtypes = [i, i, i, p, p, p, p]
                 lib.fp8_gemm_scaled.restype = i
                 lib.fp8_gemm_scaled.argtypes = [i, i, i, p, p, p, f, p, p, i, p]
+                lib.fp8_gemm_accumulate_f32.restype = i
+                lib.fp8_gemm_accumulate_f32.argtypes = [i, i, i, p, p, p, f, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
                 lib.fp8_gemm_version.restype = C.c_char_p
                 _state["lib"] = lib
@@ -76,6 +78,13 @@ def FP8GEMMScaled(M, N, K, A, B, Cptr, alpha=1.0, scale_a=0, scale_b=0, out_dtyp
     rc = _init().fp8_gemm_scaled(M, N, K, A, B, Cptr, alpha, scale_a or None, scale_b or None, out_dtype, stream)
     if rc != 0:
         raise FP8GEMMError(f"fp8_gemm_scaled: CUDA error {rc}")
+
+
+def FP8GEMMAccumulateF32(M, N, K, A, B, X, alpha=1.0, scale_a=0, scale_b=0, stream=0) -> None:
+    """X (fp32 [M, N]) += alpha * (*scale_a) * (*scale_b) * A x B^T: the residual update in the GEMM epilogue."""
+    rc = _init().fp8_gemm_accumulate_f32(M, N, K, A, B, X, alpha, scale_a or None, scale_b or None, stream or None)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_accumulate_f32: CUDA error {rc}")
 
 
 def device_status() -> int:

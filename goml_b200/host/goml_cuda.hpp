@@ -91,6 +91,7 @@ struct GemmLib {
     int (*original)(int, int, int, const void*, const void*, void*, void*) = nullptr;
     int (*ss)(int, int, int, const void*, const void*, void*, void*) = nullptr;
     int (*scaled)(int, int, int, const void*, const void*, void*, float, const float*, const float*, int, void*) = nullptr;
+    int (*accumulate)(int, int, int, const void*, const void*, float*, float, const float*, const float*, void*) = nullptr;
     int (*status)() = nullptr;
 };
 inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
@@ -104,6 +105,7 @@ inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
         g.original = sym<decltype(g.original)>(g.lib, "fp8_gemm_original");
         g.ss = sym<decltype(g.ss)>(g.lib, "fp8_gemm_singlesync");
         g.scaled = sym<decltype(g.scaled)>(g.lib, "fp8_gemm_scaled");
+        g.accumulate = sym<decltype(g.accumulate)>(g.lib, "fp8_gemm_accumulate_f32");
         g.status = sym<decltype(g.status)>(g.lib, "fp8_gemm_device_status");
     });
     if (!g.lib) throw Error(err);
@@ -124,6 +126,14 @@ inline void FP8GEMMScaled(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr
                                              reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
                                              outDType, detail::vp(stream));
     if (rc != 0) throw Error("fp8_gemm_scaled: CUDA error " + std::to_string(rc));
+}
+// X (fp32 [M,N]) += alpha * (*scaleA) * (*scaleB) * A x B^T: the residual update of a decoder block in the epilogue.
+inline void FP8GEMMAccumulateF32(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr_t X, float alpha, uintptr_t scaleA,
+                                 uintptr_t scaleB, uintptr_t stream) {
+    const int rc = detail::gemm_lib().accumulate(M, N, K, detail::vp(A), detail::vp(B), reinterpret_cast<float*>(X), alpha,
+                                                 reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
+                                                 detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm_accumulate_f32: CUDA error " + std::to_string(rc));
 }
 inline int FP8GEMMDeviceStatus() { return detail::gemm_lib().status(); }
 

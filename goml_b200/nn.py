@@ -57,6 +57,12 @@ class FP8Linear:
         M = x.numel() // self.in_features
         return self.forward_codes(quantize(x.reshape(M, self.in_features).float()), M)
 
+    def accumulate_into(self, xq: FP8Tensor, M: int, x: torch.Tensor) -> None:
+        """x (fp32 [M, out]) += this layer's output, added in the GEMM epilogue (no 16-bit intermediate)."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.shape == (M, self.out_features)
+        G.FP8GEMMAccumulateF32(M, self.out_features, self.in_features, xq.codes.data_ptr(), self.w.codes.data_ptr(), x.data_ptr(),
+                               1.0, xq.scale_ptr, self.w.scale_ptr, torch.cuda.current_stream().cuda_stream)
+
     def forward_codes(self, xq: FP8Tensor, M: int) -> torch.Tensor:
         """The GEMM alone, on an activation that is already e4m3 codes + device scale."""
         y = torch.empty((M, self.out_features), dtype=torch.bfloat16, device=xq.codes.device)
@@ -115,7 +121,8 @@ class FP8DecoderBlock:
         return self._rope[S]
 
     def forward_fused(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
-        """The block with every glue op fused with the quantiser of its consumer: 11 library calls, no torch math."""
+        """The block with every glue op fused with the quantiser of its consumer and both residual adds done in
+        the GEMM epilogues: 9 library calls, no torch math."""
         dev, T, d, H, hd, Fh = x.device, B * S, self.d, self.H, self.hd, self.F
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
@@ -136,16 +143,15 @@ class FP8DecoderBlock:
                           s3.data_ptr(), s3.data_ptr() + 4, s3.data_ptr() + 8, sh)
         oq = FP8Tensor(u8(T, d), sa())
         BG.PermuteQuantizeHeads(o.data_ptr(), oq.codes.data_ptr(), oq.sa.data_ptr(), oq.sa.data_ptr() + 4, B, S, H, hd, sh)
-        ao = self.o.forward_codes(oq, T)
-        # feed-forward half: h += ao, normalise, quantise in one op
+        self.o.accumulate_into(oq, T, h)                         # h += attention projection, in the GEMM epilogue
+        # feed-forward half
         xq2 = FP8Tensor(u8(T, d), sa())
-        BG.RMSNormQuantize(h.data_ptr(), ao.data_ptr(), h.data_ptr(), self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),
+        BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),
                            xq2.sa.data_ptr() + 4, rstd.data_ptr(), T, d, self.eps, sh)
         gu = self.gate_up.forward_codes(xq2, T)                  # [T, 2F] bf16, gate columns first
         hq = FP8Tensor(u8(T, Fh), sa())
         BG.SwiGLUQuantize(gu.data_ptr(), hq.codes.data_ptr(), hq.sa.data_ptr(), hq.sa.data_ptr() + 4, T, Fh, sh)
-        ffn = self.down.forward_codes(hq, T)
-        BG.ResidualAdd(h.data_ptr(), ffn.data_ptr(), T * d, sh)
+        self.down.accumulate_into(hq, T, h)                      # h += feed-forward output
         return h
 
     def __call__(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:

@@ -56,6 +56,14 @@ FP8GEMM_API int fp8_gemm_singlesync(int M, int N, int K, const void* A, const vo
 FP8GEMM_API int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* B, void* C, float alpha,
                                 const float* scale_a, const float* scale_b, int out_dtype, void* stream);
 
+/* Additive extension: the residual-stream update of a decoder block in the GEMM epilogue,
+ *   X[M,N] (fp32, row-major) += (alpha * (*scale_a) * (*scale_b)) * A . B^T
+ * read-modify-write with 128-bit accesses; takes the place of a 16-bit result followed by
+ * a separate add pass over X (x = x + W y in internal/abjexam/llama_hf_f64ref.go:150,178).
+ * The fp32 accumulators are added un-rounded. */
+FP8GEMM_API int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, const void* B, float* X, float alpha,
+                                        const float* scale_a, const float* scale_b, void* stream);
+
 /* Additive: device-side status of the current device.  The kernels bound every
  * wait; if a wait ever runs out they record a non-zero code here and exit
  * cleanly.  This call synchronises the device and returns (and clears) the

@@ -15,12 +15,14 @@ import numpy as np
 import oracle as O
 
 
-def _linear(x, w):
-    """bf16( sx*sw * codes(x) . codes(w)^T ), fp64 accumulation."""
+def _linear(x, w, round_out=True):
+    """bf16( sx*sw * codes(x) . codes(w)^T ), fp64 accumulation; un-rounded when the product adds the result
+    into the fp32 residual stream inside the GEMM epilogue."""
     xq, sx, _ = O.quantize_f32(x.astype(np.float32))
     wq, sw, _ = O.quantize_f32(w.astype(np.float32))
     alpha = float(np.float32(sx) * np.float32(sw))  # the kernel multiplies the fp32 scales
-    return O.round_bf16(O.gemm_f64(xq, wq, alpha)).astype(np.float64)
+    y = O.gemm_f64(xq, wq, alpha)
+    return O.round_bf16(y).astype(np.float64) if round_out else y
 
 
 def _rms_norm(x, gamma, eps):
@@ -37,9 +39,12 @@ def _rope(x, theta):  # x [B, H, S, hd]
     return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1)
 
 
-def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0, intermediates=None):
+def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0, intermediates=None,
+                  residual_in_epilogue=False):
     """Returns the block output [B*S, d] (fp64).  When `intermediates` is a dict it receives the input of
-    every quantised stage and that stage's output, so each product stage can be checked on identical inputs."""
+    every quantised stage and that stage's output, so each product stage can be checked on identical inputs.
+    `residual_in_epilogue`: the O and down projections are added to the stream un-rounded (fp32 accumulators),
+    as the product's fused path does; otherwise they are rounded to bf16 first."""
     x = x.astype(np.float64)
     d = x.shape[1]
     hd = d // H
@@ -53,12 +58,12 @@ def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5,
     scale = float(np.float32(1.0 / math.sqrt(hd)) * np.float32(sq) * np.float32(sk))
     o, _ = O.attention_f64(qq, kq, vq, 1, 0, scale, float(sv))
     keep["attn"] = O.round_fp16(o).astype(np.float64).reshape(B, H, S, hd).transpose(0, 2, 1, 3).reshape(B * S, d)
-    keep["ao"] = _linear(keep["attn"], wo)
+    keep["ao"] = _linear(keep["attn"], wo, round_out=not residual_in_epilogue)
     x = x + keep["ao"]
     keep["x_mid"] = x
     keep["xn2"] = _rms_norm(x, norm2, eps)
     keep["gu"] = _linear(keep["xn2"], wgate_up)
     g, u = keep["gu"][:, :Fh], keep["gu"][:, Fh:]
     keep["h"] = g / (1.0 + np.exp(-g)) * u
-    keep["ffn"] = _linear(keep["h"], wdown)
+    keep["ffn"] = _linear(keep["h"], wdown, round_out=not residual_in_epilogue)
     return x + keep["ffn"]

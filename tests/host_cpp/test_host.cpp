@@ -41,6 +41,7 @@ static int run_cpu(const char* libs_dir) {
     // error text (fp8_gemm.go:57-61): CUDA error code in the message
     CHECK(thrown([] { FP8GEMM(8, 8, 24, 16, 16, 16, ModeSinglesync, 0); }) == "fp8_gemm: CUDA error 1");
     CHECK(thrown([] { FP8GEMMScaled(8, 8, 32, 16, 16, 16, 1.0f, 0, 0, 9, 0); }) == "fp8_gemm_scaled: CUDA error 1");
+    CHECK(thrown([] { FP8GEMMAccumulateF32(8, 8, 32, 16, 16, 0, 1.0f, 0, 0, 0); }) == "fp8_gemm_accumulate_f32: CUDA error 1");
     // status strings and dispatcher (fa_forward.go:36-60; libs/fa_sm120/go/gofa/gofa_test.go:15-37)
     FALoad();
     CHECK(FAStatusString(FA_OK) == "OK");

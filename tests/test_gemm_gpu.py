@@ -121,3 +121,24 @@ def test_config2_full_size_on_sampled_rows(cuda, built_libs):
     G.FP8GEMMScaled(n, n, n, ad[perm].contiguous().data_ptr(), bd.data_ptr(), c3.data_ptr(), alpha, 0, 0, G.OutBF16, 0)
     torch.cuda.synchronize()
     assert torch.equal(c3, c[perm])
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 144), (129, 257, 160), (16, 8192, 256)])
+def test_accumulate_into_fp32(cuda, built_libs, M, N, K):
+    # the residual-stream update in the epilogue: X += alpha * sa * sb * A.B^T, fp32 accumulators added un-rounded
+    from goml_b200 import fp8_gemm as G
+    cfg = f"acc{M}x{N}x{K}"
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (M, K), config=cfg))
+    b, sb, _ = O.quantize_f32(O.seeded_normal("B", (N, K), config=cfg))
+    x = O.seeded_normal("X", (M, N), config=cfg).astype(np.float32)
+    ad, bd = dev_u8(a), dev_u8(b)
+    xd = torch.from_numpy(x.copy()).cuda()
+    scales = torch.tensor([float(sa), float(sb)], dtype=torch.float32, device="cuda")
+    G.FP8GEMMAccumulateF32(M, N, K, ad.data_ptr(), bd.data_ptr(), xd.data_ptr(), 0.5, scales.data_ptr(), scales.data_ptr() + 4)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    prod = O.gemm_f64(a, b, 0.5 * float(np.float32(sa) * np.float32(sb)))
+    ref = x.astype(np.float64) + prod
+    got = xd.double().cpu().numpy()
+    rms = float(np.sqrt(np.mean(prod ** 2)))
+    assert np.abs(got - ref).max() <= 1e-5 * max(rms, 1.0) * np.sqrt(K), np.abs(got - ref).max()
