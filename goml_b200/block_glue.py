@@ -34,6 +34,7 @@ def _init():
                 "fp8_rope_quantize_qkv": [p, p, p, p, p, p, p, p, i, i, i, i, p],
                 "fp8_permute_quantize_heads": [p, p, p, p, i, i, i, i, p],
                 "fp8_swiglu_quantize": [p, p, p, p, i, i, p],
+                "fp8_quantize_bf16": [p, p, p, p, z, p],
                 "fp8_residual_add": [p, p, z, p],
             }.items():
                 fn = getattr(lib, name)
@@ -72,6 +73,10 @@ def PermuteQuantizeHeads(o_fp16: int, q: int, scale: int, amax: int, batch: int,
 
 def SwiGLUQuantize(gate_up_bf16: int, q: int, scale: int, amax: int, rows: int, ffn_hidden: int, stream: int = 0) -> None:
     _check("fp8_swiglu_quantize", _init().fp8_swiglu_quantize(gate_up_bf16, q, scale, amax, rows, ffn_hidden, stream or None))
+
+
+def QuantizeBF16(x_bf16: int, q: int, scale: int, amax_in: int, n: int, stream: int = 0) -> None:
+    _check("fp8_quantize_bf16", _init().fp8_quantize_bf16(x_bf16, q, scale, amax_in, n, stream or None))
 
 
 def ResidualAdd(x: int, y_bf16: int, n: int, stream: int = 0) -> None:

@@ -556,6 +556,28 @@ __global__ void __launch_bounds__(THREADS) swiglu_quant_kernel(const uint16_t* _
     }
 }
 
+// ---------------------------------------------------------------------------------- quantise bf16 with a known amax
+// single pass: the producer (the SwiGLU GEMM epilogue) already reduced max|x|
+__global__ void __launch_bounds__(THREADS) quant_bf16_kernel(const uint16_t* __restrict__ x, const float* __restrict__ amax_ptr,
+                                                             float* scale_out, uint8_t* __restrict__ q, size_t n16) {
+    const float scale = scale_from_amax(*amax_ptr);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < n16; it += 2 * stride) {  // two items per step, loads first
+        const bool second = it + stride < n16;
+        const U8 a = ldg256(x + it * 16);
+        const U8 b = ldg256(x + (second ? it + stride : it) * 16);
+        float y[16];
+        bf16x16_to_f32(a, y);
+        *reinterpret_cast<uint4*>(q + it * 16) = quant16(y, inv);
+        if (second) {
+            bf16x16_to_f32(b, y);
+            *reinterpret_cast<uint4*>(q + (it + stride) * 16) = quant16(y, inv);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- residual add
 __global__ void __launch_bounds__(THREADS) residual_add_kernel(float* __restrict__ x, const uint16_t* __restrict__ y, size_t n8) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
@@ -672,6 +694,13 @@ int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, 
     const FastDiv per_row(ffn_hidden / 16);
     if (items > 0) swiglu_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, (uint32_t)items, ffn_hidden, per_row);
     swiglu_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, amax_out, scale_out, q, (uint32_t)items, ffn_hidden, per_row);
+    return (int)cudaGetLastError();
+}
+
+int fp8_quantize_bf16(const void* x_bf16, uint8_t* q, float* scale_out, const float* amax_in, size_t n, void* stream) {
+    if (!x_bf16 || !q || !scale_out || !amax_in || (n % 16) != 0 || misaligned32(x_bf16) || misaligned(q)) return (int)cudaErrorInvalidValue;
+    quant_bf16_kernel<<<grid_for(n / 32 + 1), THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint16_t*>(x_bf16), amax_in, scale_out, q,
+                                                                                 n / 16);
     return (int)cudaGetLastError();
 }
 

@@ -67,6 +67,11 @@ struct GemmParams {
     const float* scale_b;
     int out_bf16;
     float* X;  // when set: X[M,N] (fp32) += alpha * A.B^T instead of storing C (the residual-stream update of a decoder block)
+    // SwiGLU mode (BN = 256 only): B holds 128 gate rows then the 128 matching up rows per 256-row tile; the epilogue
+    // writes H[M, F] = silu(alpha*gate) * (alpha*up) as bf16 and reduces max|H| into *amax
+    void* H;
+    int F;
+    float* amax;
     int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
     int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
@@ -235,6 +240,53 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const int row = tm * BM + row_in_tile;
             const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
+            if (BN == 256 && p.H) {
+                // gate columns [0,128) and up columns [128,256) of the accumulator -> 128 activations per row
+                uint16_t* hrow = reinterpret_cast<uint16_t*>(p.H) + (size_t)row * p.F;
+                const bool hvec_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.H) & 15) == 0);
+                float tmax = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    const int col0 = (n0 >> 1) + c * 32;   // activation column of this chunk
+                    if (col0 >= p.F) break;                 // uniform across the CTA
+                    uint32_t g[32], uacc[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, g);
+                    tmem_ld_32x32b_x32(taddr + 128 + c * 32, uacc);
+                    tmem_ld_wait();
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        float h[2];
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const float gv = __uint_as_float(g[2 * j + e]) * alpha;
+                            const float uv = __uint_as_float(uacc[2 * j + e]) * alpha;
+                            float r;
+                            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + __expf(-gv)));
+                            h[e] = gv * r * uv;
+                        }
+                        const __nv_bfloat162 hb = __floats2bfloat162_rn(h[0], h[1]);
+                        w[j] = *reinterpret_cast<const uint32_t*>(&hb);
+                        // max of the rounded values = what the quantiser that follows will see
+                        tmax = fmaxf(tmax, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xffff0000u))));
+                    }
+                    if (row < p.M) {
+                        if (hvec_ok && col0 + 32 <= p.F) {
+                            uint4* dst = reinterpret_cast<uint4*>(hrow + col0);
+#pragma unroll
+                            for (int v = 0; v < 4; v++) dst[v] = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < p.F) hrow[col0 + j] = (uint16_t)((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
+                        }
+                    }
+                }
+                // rows >= M and columns >= F hold zeros (zero-filled operand rows): they never raise the maximum
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+                if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
+            } else
 #pragma unroll 1
             for (int c = 0; c < bn / 32; c++) {
                 const int col0 = n0 + c * 32;
@@ -342,10 +394,11 @@ constexpr int MAX_DEVICES = 64;
 DeviceState g_dev[MAX_DEVICES];
 
 int launch(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* sa, const float* sb,
-           int out_bf16, cudaStream_t stream, float* X = nullptr) {
+           int out_bf16, cudaStream_t stream, float* X = nullptr, void* H = nullptr, int F = 0, float* amax = nullptr) {
     if (M < 0 || N < 0 || K < 0) return (int)cudaErrorInvalidValue;
     if (M == 0 || N == 0) return 0;
-    if (!A || !B || (!C && !X)) return (int)cudaErrorInvalidValue;
+    if (!A || !B || (!C && !X && !H)) return (int)cudaErrorInvalidValue;
+    if (H && (!amax || F <= 0 || N != 2 * ((F + 127) / 128) * 128 || (reinterpret_cast<uintptr_t>(H) & 1))) return (int)cudaErrorInvalidValue;
     if (K == 0 || (K % 16) != 0) return (int)cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
         (reinterpret_cast<uintptr_t>(C) & 1) || (reinterpret_cast<uintptr_t>(X) & 3))
@@ -381,13 +434,16 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     };
     int bn = 256;
     long long best = estimate(256, 128) * 3 / 4;
-    if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
-    if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
+    if (!H) {  // the SwiGLU epilogue needs gate and up columns of a row in one 256-wide tile
+        if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
+        if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
+    }
 
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
     p.X = X;
+    p.H = H; p.F = F; p.amax = amax;
     p.x_tma = (X && (N % 4) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) ? 1 : 0;
     p.m_tiles = (int)m_tiles;
     p.n_tiles = (N + bn - 1) / bn;
@@ -398,7 +454,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles >= (1ll << 30)) return (int)cudaErrorInvalidValue;
     const int rem = (int)(tiles % st.num_sms);
-    const bool split_tail = (bn == 256) && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
+    const bool split_tail = (bn == 256) && !H && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
     p.split_from = (int)(split_tail ? tiles - rem : tiles);
     p.num_units = (int)(split_tail ? tiles + rem : tiles);
 
@@ -445,6 +501,15 @@ int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, const void* B, f
                             const float* scale_b, void* stream) {
     if (!X) return (int)cudaErrorInvalidValue;
     return launch(M, N, K, A, B, nullptr, alpha, scale_a, scale_b, 0, (cudaStream_t)stream, X);
+}
+
+int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleaved, void* H, float alpha, const float* scale_a,
+                    const float* scale_b, float* amax_out, void* stream) {
+    if (!H || !amax_out || F <= 0) return (int)cudaErrorInvalidValue;
+    cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    const int n = 2 * ((F + 127) / 128) * 128;
+    return launch(M, n, K, A, B_interleaved, nullptr, alpha, scale_a, scale_b, 1, (cudaStream_t)stream, nullptr, H, F, amax_out);
 }
 
 int fp8_gemm_device_status(void) {

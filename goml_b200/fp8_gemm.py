@@ -44,6 +44,8 @@ def _init():
                 lib.fp8_gemm_scaled.argtypes = [i, i, i, p, p, p, f, p, p, i, p]
                 lib.fp8_gemm_accumulate_f32.restype = i
                 lib.fp8_gemm_accumulate_f32.argtypes = [i, i, i, p, p, p, f, p, p, p]
+                lib.fp8_gemm_swiglu.restype = i
+                lib.fp8_gemm_swiglu.argtypes = [i, i, i, p, p, p, f, p, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
                 lib.fp8_gemm_version.restype = C.c_char_p
                 _state["lib"] = lib
@@ -85,6 +87,26 @@ def FP8GEMMAccumulateF32(M, N, K, A, B, X, alpha=1.0, scale_a=0, scale_b=0, stre
     rc = _init().fp8_gemm_accumulate_f32(M, N, K, A, B, X, alpha, scale_a or None, scale_b or None, stream or None)
     if rc != 0:
         raise FP8GEMMError(f"fp8_gemm_accumulate_f32: CUDA error {rc}")
+
+
+def FP8GEMMSwiGLU(M, F, K, A, B_interleaved, H, alpha=1.0, scale_a=0, scale_b=0, amax_out=0, stream=0) -> None:
+    """H (bf16 [M, F]) = silu(g) * u with [g | u] = alpha * sa * sb * A x B_interleaved^T; max|H| -> *amax_out."""
+    rc = _init().fp8_gemm_swiglu(M, F, K, A, B_interleaved, H, alpha, scale_a or None, scale_b or None, amax_out, stream or None)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_swiglu: CUDA error {rc}")
+
+
+def interleave_gate_up(w_gate_up, F: int):
+    """[2F, K] (gate rows first) -> the [2*Fp, K] layout fp8_gemm_swiglu reads: per 128 feed-forward columns, the
+    128 gate rows followed by the 128 up rows; rows past F are zero.  Works on torch tensors and numpy arrays."""
+    Fp = (F + 127) // 128 * 128
+    K = w_gate_up.shape[1]
+    out = w_gate_up.new_zeros((2 * Fp, K)) if hasattr(w_gate_up, "new_zeros") else __import__("numpy").zeros((2 * Fp, K), w_gate_up.dtype)
+    for t in range(Fp // 128):
+        lo, hi = 128 * t, min(128 * t + 128, F)
+        out[256 * t: 256 * t + (hi - lo)] = w_gate_up[lo:hi]
+        out[256 * t + 128: 256 * t + 128 + (hi - lo)] = w_gate_up[F + lo: F + hi]
+    return out
 
 
 def device_status() -> int:

@@ -97,6 +97,8 @@ class FP8DecoderBlock:
         assert self.hd in (64, 128)
         self.qkv, self.o = FP8Linear(wqkv), FP8Linear(wo)
         self.gate_up, self.down = FP8Linear(wgate_up), FP8Linear(wdown)
+        # the same gate/up codes in the layout the SwiGLU GEMM epilogue reads (gate and up rows of a column block adjacent)
+        self.gate_up_interleaved = G.interleave_gate_up(self.gate_up.w.codes, ffn_hidden)
         self.norm1, self.norm2 = norm1.float(), norm2.float()
         self.eps, self.theta = eps, theta
         self.fa = F.FACreate()
@@ -122,7 +124,7 @@ class FP8DecoderBlock:
 
     def forward_fused(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
         """The block with every glue op fused with the quantiser of its consumer and both residual adds done in
-        the GEMM epilogues: 9 library calls, no torch math."""
+        the GEMM epilogues, SwiGLU in the gate/up GEMM's epilogue: 9 library calls, no torch math."""
         dev, T, d, H, hd, Fh = x.device, B * S, self.d, self.H, self.hd, self.F
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
@@ -148,9 +150,12 @@ class FP8DecoderBlock:
         xq2 = FP8Tensor(u8(T, d), sa())
         BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),
                            xq2.sa.data_ptr() + 4, rstd.data_ptr(), T, d, self.eps, sh)
-        gu = self.gate_up.forward_codes(xq2, T)                  # [T, 2F] bf16, gate columns first
         hq = FP8Tensor(u8(T, Fh), sa())
-        BG.SwiGLUQuantize(gu.data_ptr(), hq.codes.data_ptr(), hq.sa.data_ptr(), hq.sa.data_ptr() + 4, T, Fh, sh)
+        hb = torch.empty((T, Fh), dtype=torch.bfloat16, device=dev)
+        # gate/up projections with silu(gate) * up and max|.| in the GEMM epilogue, then one quantiser pass
+        G.FP8GEMMSwiGLU(T, Fh, d, xq2.codes.data_ptr(), self.gate_up_interleaved.data_ptr(), hb.data_ptr(), 1.0, xq2.scale_ptr,
+                        self.gate_up.w.scale_ptr, hq.sa.data_ptr() + 4, sh)
+        BG.QuantizeBF16(hb.data_ptr(), hq.codes.data_ptr(), hq.sa.data_ptr(), hq.sa.data_ptr() + 4, T * Fh, sh)
         self.down.accumulate_into(hq, T, h)                      # h += feed-forward output
         return h
 

@@ -77,6 +77,12 @@ FP8BLOCK_API int fp8_permute_quantize_heads(const void* o_fp16, uint8_t* q, floa
 FP8BLOCK_API int fp8_swiglu_quantize(const void* gate_up_bf16, uint8_t* q, float* scale_out, float* amax_out, int rows,
                                      int ffn_hidden, void* stream);
 
+/* Single-pass quantiser for a bf16 tensor whose max|x| the producer already reduced into *amax_in (the SwiGLU
+ * epilogue of fp8_gemm_swiglu does): scale = amax/448 as above, *scale_out written.  n a multiple of 16,
+ * x 32-byte aligned. */
+FP8BLOCK_API int fp8_quantize_bf16(const void* x_bf16, uint8_t* q, float* scale_out, const float* amax_in, size_t n,
+                                   void* stream);
+
 /* x[i] += y[i] (x fp32 residual stream, y bf16), n a multiple of 8. */
 FP8BLOCK_API int fp8_residual_add(float* x, const void* y_bf16, size_t n, void* stream);
 

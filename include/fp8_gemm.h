@@ -64,6 +64,16 @@ FP8GEMM_API int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* 
 FP8GEMM_API int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, const void* B, float* X, float alpha,
                                         const float* scale_a, const float* scale_b, void* stream);
 
+/* Additive extension: the SwiGLU feed-forward's gate and up projections with the activation in the epilogue,
+ *   H[M,F] (bf16) = silu(g) * u,   g = s * A . Wgate^T,   u = s * A . Wup^T,   s = alpha * (*scale_a) * (*scale_b)
+ * (silu(x) = x / (1 + e^-x); nn/feedforward.go:54-79 computes W2(silu(W1 x) * W3 x)), and max|H| reduced into
+ * *amax_out (cleared by the call) for the per-tensor quantiser of the down projection's operand.
+ * B_interleaved holds both weights, [2 * Fp, K] with Fp = F rounded up to 128: rows [256t, 256t+128) are rows
+ * [128t, 128t+128) of Wgate, rows [256t+128, 256t+256) the same rows of Wup; rows past F are zero.
+ * The 16-bit gate/up matrix is never written. */
+FP8GEMM_API int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleaved, void* H, float alpha,
+                                const float* scale_a, const float* scale_b, float* amax_out, void* stream);
+
 /* Additive: device-side status of the current device.  The kernels bound every
  * wait; if a wait ever runs out they record a non-zero code here and exit
  * cleanly.  This call synchronises the device and returns (and clears) the

@@ -40,11 +40,12 @@ def _rope(x, theta):  # x [B, H, S, hd]
 
 
 def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5, theta=10000.0, intermediates=None,
-                  residual_in_epilogue=False):
+                  residual_in_epilogue=False, swiglu_in_epilogue=False):
     """Returns the block output [B*S, d] (fp64).  When `intermediates` is a dict it receives the input of
     every quantised stage and that stage's output, so each product stage can be checked on identical inputs.
     `residual_in_epilogue`: the O and down projections are added to the stream un-rounded (fp32 accumulators),
-    as the product's fused path does; otherwise they are rounded to bf16 first."""
+    as the product's fused path does; otherwise they are rounded to bf16 first.
+    `swiglu_in_epilogue`: silu(gate) * up is taken on the un-rounded gate/up projections and rounded to bf16 once."""
     x = x.astype(np.float64)
     d = x.shape[1]
     hd = d // H
@@ -62,8 +63,10 @@ def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5,
     x = x + keep["ao"]
     keep["x_mid"] = x
     keep["xn2"] = _rms_norm(x, norm2, eps)
-    keep["gu"] = _linear(keep["xn2"], wgate_up)
+    keep["gu"] = _linear(keep["xn2"], wgate_up, round_out=not swiglu_in_epilogue)
     g, u = keep["gu"][:, :Fh], keep["gu"][:, Fh:]
     keep["h"] = g / (1.0 + np.exp(-g)) * u
+    if swiglu_in_epilogue:
+        keep["h"] = O.round_bf16(keep["h"]).astype(np.float64)
     keep["ffn"] = _linear(keep["h"], wdown, round_out=not residual_in_epilogue)
     return x + keep["ffn"]

@@ -35,7 +35,7 @@ def test_block_matches_cpu_restatement(cuda, built_libs, B, S, d, H, Fh, fused):
     blk.fa.DeviceStatus()
     blk.close()
     got = y.double().cpu().numpy()
-    ref = decoder_block(x, B, S, H, w["wqkv"], w["wo"], w["wgate_up"], w["wdown"], g1, g2, residual_in_epilogue=fused)
+    ref = decoder_block(x, B, S, H, w["wqkv"], w["wo"], w["wgate_up"], w["wdown"], g1, g2, residual_in_epilogue=fused, swiglu_in_epilogue=fused)
     assert np.isfinite(got).all()
     maxabs, meanrel = O.error_stats(got, ref)
     assert maxabs <= 2e-2 and meanrel <= 1e-2, (maxabs, meanrel)

@@ -142,3 +142,32 @@ def test_accumulate_into_fp32(cuda, built_libs, M, N, K):
     got = xd.double().cpu().numpy()
     rms = float(np.sqrt(np.mean(prod ** 2)))
     assert np.abs(got - ref).max() <= 1e-5 * max(rms, 1.0) * np.sqrt(K), np.abs(got - ref).max()
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 1376, 512), (130, 704, 256), (64, 11008, 128), (300, 128, 144)])
+def test_swiglu_epilogue(cuda, built_libs, M, F, K):
+    # gate/up projections with silu(gate) * up in the epilogue: bf16 H, max|H| exact, and the quantiser pass that follows
+    from goml_b200 import fp8_gemm as G, block_glue as BG
+    cfg = f"swiglu{M}x{F}x{K}"
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (M, K), config=cfg))
+    w, sw, _ = O.quantize_f32(O.seeded_normal("W", (2 * F, K), std=0.08, config=cfg))
+    wi = G.interleave_gate_up(w, F)
+    ad, wd = dev_u8(a), dev_u8(wi)
+    h = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scales = torch.tensor([float(sa), float(sw)], dtype=torch.float32, device="cuda")
+    s2 = torch.full((2,), 5.0, dtype=torch.float32, device="cuda")
+    G.FP8GEMMSwiGLU(M, F, K, ad.data_ptr(), wd.data_ptr(), h.data_ptr(), 1.0, scales.data_ptr(), scales.data_ptr() + 4, s2.data_ptr() + 4)
+    q = torch.full((M, F), 0xAA, dtype=torch.uint8, device="cuda")
+    BG.QuantizeBF16(h.data_ptr(), q.data_ptr(), s2.data_ptr(), s2.data_ptr() + 4, M * F)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    gu = O.gemm_f64(a, w, float(np.float32(sa) * np.float32(sw)))
+    g, u = gu[:, :F], gu[:, F:]
+    ref = g / (1.0 + np.exp(-g)) * u
+    got = h.double().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.all(np.abs(got - ref) <= 2.0 ** -7 * np.abs(ref) + 1e-6 * np.abs(ref).max())
+    hv = h.float().cpu().numpy()
+    assert s2[1].item() == np.abs(hv).max()                       # the epilogue's amax is the max of what it wrote
+    codes, scale, amax = O.quantize_f32(np.ascontiguousarray(hv))
+    assert s2[0].item() == scale and np.array_equal(q.cpu().numpy(), codes)   # quantiser pass bit-exact on those values
