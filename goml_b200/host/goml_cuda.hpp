@@ -92,6 +92,7 @@ struct GemmLib {
     int (*ss)(int, int, int, const void*, const void*, void*, void*) = nullptr;
     int (*scaled)(int, int, int, const void*, const void*, void*, float, const float*, const float*, int, void*) = nullptr;
     int (*accumulate)(int, int, int, const void*, const void*, float*, float, const float*, const float*, void*) = nullptr;
+    int (*swiglu)(int, int, int, const void*, const void*, void*, float, const float*, const float*, float*, void*) = nullptr;
     int (*status)() = nullptr;
 };
 inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
@@ -106,6 +107,7 @@ inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
         g.ss = sym<decltype(g.ss)>(g.lib, "fp8_gemm_singlesync");
         g.scaled = sym<decltype(g.scaled)>(g.lib, "fp8_gemm_scaled");
         g.accumulate = sym<decltype(g.accumulate)>(g.lib, "fp8_gemm_accumulate_f32");
+        g.swiglu = sym<decltype(g.swiglu)>(g.lib, "fp8_gemm_swiglu");
         g.status = sym<decltype(g.status)>(g.lib, "fp8_gemm_device_status");
     });
     if (!g.lib) throw Error(err);
@@ -134,6 +136,27 @@ inline void FP8GEMMAccumulateF32(int M, int N, int K, uintptr_t A, uintptr_t B, 
                                                  reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
                                                  detail::vp(stream));
     if (rc != 0) throw Error("fp8_gemm_accumulate_f32: CUDA error " + std::to_string(rc));
+}
+// H (bf16 [M,F]) = silu(g) * u, [g | u] = alpha * (*scaleA) * (*scaleB) * A x Binterleaved^T; max|H| -> *amaxOut.
+// Binterleaved: per 128 feed-forward columns the 128 gate rows then the 128 up rows (InterleaveGateUp below).
+inline void FP8GEMMSwiGLU(int M, int F, int K, uintptr_t A, uintptr_t Binterleaved, uintptr_t H, float alpha, uintptr_t scaleA,
+                          uintptr_t scaleB, uintptr_t amaxOut, uintptr_t stream) {
+    const int rc = detail::gemm_lib().swiglu(M, F, K, detail::vp(A), detail::vp(Binterleaved), detail::vp(H), alpha,
+                                             reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
+                                             reinterpret_cast<float*>(amaxOut), detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm_swiglu: CUDA error " + std::to_string(rc));
+}
+// Host-side weight preparation for FP8GEMMSwiGLU: codes [2F, K] (gate rows first) -> [2*Fp, K], Fp = F rounded up to 128.
+inline std::vector<uint8_t> InterleaveGateUp(const std::vector<uint8_t>& gateUp, int F, int K) {
+    const int Fp = (F + 127) / 128 * 128;
+    std::vector<uint8_t> out((size_t)2 * Fp * K, 0);
+    for (int t = 0; t < Fp / 128; t++)
+        for (int r = 0; r < 128 && 128 * t + r < F; r++) {
+            std::copy(gateUp.begin() + (size_t)(128 * t + r) * K, gateUp.begin() + (size_t)(128 * t + r + 1) * K, out.begin() + (size_t)(256 * t + r) * K);
+            std::copy(gateUp.begin() + (size_t)(F + 128 * t + r) * K, gateUp.begin() + (size_t)(F + 128 * t + r + 1) * K,
+                      out.begin() + (size_t)(256 * t + 128 + r) * K);
+        }
+    return out;
 }
 inline int FP8GEMMDeviceStatus() { return detail::gemm_lib().status(); }
 
@@ -298,6 +321,7 @@ struct BlockLib {
     int (*rope_q)(const void*, const float*, const float*, uint8_t*, uint8_t*, uint8_t*, float*, float*, int, int, int, int, void*) = nullptr;
     int (*permute_q)(const void*, uint8_t*, float*, float*, int, int, int, int, void*) = nullptr;
     int (*swiglu_q)(const void*, uint8_t*, float*, float*, int, int, void*) = nullptr;
+    int (*quant_bf16)(const void*, uint8_t*, float*, const float*, size_t, void*) = nullptr;
     int (*residual_add)(float*, const void*, size_t, void*) = nullptr;
 };
 inline BlockLib& block_lib() {
@@ -312,6 +336,7 @@ inline BlockLib& block_lib() {
         b.rope_q = sym<decltype(b.rope_q)>(b.lib, "fp8_rope_quantize_qkv");
         b.permute_q = sym<decltype(b.permute_q)>(b.lib, "fp8_permute_quantize_heads");
         b.swiglu_q = sym<decltype(b.swiglu_q)>(b.lib, "fp8_swiglu_quantize");
+        b.quant_bf16 = sym<decltype(b.quant_bf16)>(b.lib, "fp8_quantize_bf16");
         b.residual_add = sym<decltype(b.residual_add)>(b.lib, "fp8_residual_add");
     });
     if (!b.lib) throw Error(err);
@@ -349,6 +374,10 @@ inline void PermuteQuantizeHeads(uintptr_t oFP16, uintptr_t q, uintptr_t scale, 
 inline void SwiGLUQuantize(uintptr_t gateUpBF16, uintptr_t q, uintptr_t scale, uintptr_t amax, int rows, int ffnHidden, uintptr_t stream = 0) {
     detail::block_check("fp8_swiglu_quantize", detail::block_lib().swiglu_q(detail::vp(gateUpBF16), detail::tp<uint8_t>(q), detail::tp<float>(scale),
                                                                              detail::tp<float>(amax), rows, ffnHidden, detail::vp(stream)));
+}
+inline void QuantizeBF16(uintptr_t xBF16, uintptr_t q, uintptr_t scale, uintptr_t amaxIn, size_t n, uintptr_t stream = 0) {
+    detail::block_check("fp8_quantize_bf16", detail::block_lib().quant_bf16(detail::vp(xBF16), detail::tp<uint8_t>(q), detail::tp<float>(scale),
+                                                                           detail::tp<const float>(amaxIn), n, detail::vp(stream)));
 }
 inline void ResidualAdd(uintptr_t x, uintptr_t yBF16, size_t n, uintptr_t stream = 0) {
     detail::block_check("fp8_residual_add", detail::block_lib().residual_add(detail::tp<float>(x), detail::vp(yBF16), n, detail::vp(stream)));

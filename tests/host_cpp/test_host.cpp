@@ -64,6 +64,16 @@ static int run_cpu(const char* libs_dir) {
     // block glue: argument errors before any launch, same message shape
     CHECK(thrown([] { SwiGLUQuantize(64, 64, 64, 64, 2, 40, 0); }) == "fp8_swiglu_quantize: CUDA error 1");
     CHECK(thrown([] { ResidualAdd(64, 64, 12, 0); }) == "fp8_residual_add: CUDA error 1");
+    CHECK(thrown([] { FP8GEMMSwiGLU(8, 0, 32, 16, 16, 16, 1.0f, 0, 0, 16, 0); }) == "fp8_gemm_swiglu: CUDA error 1");
+    {   // weight layout for the SwiGLU GEMM: F = 130 -> two column blocks, the second one mostly padding
+        const int F = 130, K = 4;
+        std::vector<uint8_t> w((size_t)2 * F * K);
+        for (size_t i = 0; i < w.size(); i++) w[i] = (uint8_t)(i / K + 1);   // row index + 1 in every byte of a row
+        const auto wi = InterleaveGateUp(w, F, K);
+        CHECK(wi.size() == (size_t)2 * 256 * K);
+        CHECK(wi[0] == 1 && wi[(size_t)127 * K] == 128 && wi[(size_t)128 * K] == (uint8_t)(F + 1) && wi[(size_t)256 * K] == 129 &&
+              wi[(size_t)257 * K] == 130 && wi[(size_t)258 * K] == 0 && wi[(size_t)384 * K] == (uint8_t)(F + 129) && wi[(size_t)386 * K] == 0);
+    }
     return fails;
 }
 
