@@ -386,7 +386,8 @@ def main():
                      "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS},
         "e2e": {"value": flops_step * world / e2e_ms / 1e9, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * (int(do_attn) + int(do_gemm)),
+        # kernels launched inside the timed region: the attention entry launches two (fp16-V pre-pass + forward), the GEMM one
+        "gpu_launches": args.steps * (2 * int(do_attn) + int(do_gemm)),
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

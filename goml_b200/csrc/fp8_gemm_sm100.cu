@@ -44,8 +44,12 @@ constexpr int STAGING_BYTES = 4 * 2 * STAGING_BOX;
 template <int BN>
 struct Tile {
     static constexpr int B_BYTES = BN * BK;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+    // The narrow tile serves HBM-bound problems whose MMAs take only 192 clk per k-block: there the producer's and the
+    // issuer's per-stage work (a wait, an expect / a commit) is the bound, so a stage holds two k-blocks.
+    static constexpr int KSUB = (BN == 64) ? 2 : 1;
+    static constexpr int SUB_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = KSUB * SUB_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 4;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers (a power of two >= 32)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -124,6 +128,9 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     constexpr int STAGES = Tile<BN>::STAGES;
     constexpr int STAGE_BYTES = Tile<BN>::STAGE_BYTES;
     constexpr int TMEM_COLS = Tile<BN>::TMEM_COLS;
+    constexpr int KSUB = Tile<BN>::KSUB;
+    constexpr int SUB_BYTES = Tile<BN>::SUB_BYTES;
+    const int k_stages = (p.k_blocks + KSUB - 1) / KSUB;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle atom = 8 rows x 128 B)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -175,13 +182,18 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 int tm, n0, bn;
                 unit_coords<BN>(u, p, tm, n0, bn);
                 const CUtensorMap* tb = (bn == BN) ? &tmap_b : &tmap_b_half;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
-                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
-                    mbar_arrive_expect_tx(fb, A_BYTES + bn * BK);
-                    tma_load_2d(sa, &tmap_a, fb, kb * BK, tm * BM);
-                    tma_load_2d(sa + A_BYTES, tb, fb, kb * BK, n0);
+                    mbar_arrive_expect_tx(fb, KSUB * (A_BYTES + bn * BK));
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; sub++) {
+                        // a k-block past the end of K (odd count) is a fully out-of-range box: zero-filled, bytes still counted
+                        const int kb = ks * KSUB + sub;
+                        const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
+                        tma_load_2d(sa, &tmap_a, fb, kb * BK, tm * BM);
+                        tma_load_2d(sa + A_BYTES, tb, fb, kb * BK, n0);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -201,16 +213,19 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 tphase[buf] ^= 1;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int ks = 0; ks < k_stages; ks++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
-                    const uint64_t adesc = kmajor_desc_sw128(sa);
-                    const uint64_t bdesc = kmajor_desc_sw128(sa + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 32; k++) {
-                        // +32 bytes along K inside the swizzle span = +2 in the address field
-                        mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                    for (int sub = 0; sub < KSUB; sub++) {
+                        const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
+                        const uint64_t adesc = kmajor_desc_sw128(sa);
+                        const uint64_t bdesc = kmajor_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / 32; k++) {
+                            // +32 bytes along K inside the swizzle span = +2 in the address field
+                            mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | sub | k) != 0);
+                        }
                     }
                     mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
