@@ -6,7 +6,7 @@
 // same argument meaning and return convention), rebuilt around the Blackwell
 // data path instead of mma.sync:
 //
-//   TMA (128-byte swizzle) -> 4-stage shared-memory ring under mbarriers
+//   TMA (128-byte swizzle) -> 4-stage shared-memory ring under mbarriers (6 stages / 4 double stages for the narrower tiles)
 //     -> one thread issues tcgen05.mma kind::f8f6f4 (M128 x N256 x K32), FP32
 //        accumulators in tensor memory, double buffered (2 x 256 columns)
 //     -> 4 epilogue warps read TMEM (tcgen05.ld), scale, convert and store with
