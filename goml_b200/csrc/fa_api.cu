@@ -183,6 +183,49 @@ fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* g) {
     return run(ctx, "fa_forward_ex", a);
 }
 
+fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* g) {
+    const char* who = "fa_decode";
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    if (!g) { set_err(ctx, "%s: null argument block", who); return FA_ERR_INVALID_ARG; }
+    if (!ctx->arch_ok || !ctx->has_pool) { set_err(ctx, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
+    if (!g->q || !g->k_cache || !g->v_cache || !g->o) { set_err(ctx, "%s: null pointer in q/k_cache/v_cache/o", who); return FA_ERR_INVALID_ARG; }
+    if (g->batch <= 0 || g->q_heads <= 0 || g->kv_heads <= 0 || g->s_max <= 0) { set_err(ctx, "%s: batch/heads/s_max must be > 0", who); return FA_ERR_INVALID_ARG; }
+    if (g->head_dim != 64 && g->head_dim != 128) { set_err(ctx, "%s: head_dim must be 64 or 128", who); return FA_ERR_UNSUPPORTED_HD; }
+    if (g->q_heads % g->kv_heads != 0 || g->q_heads / g->kv_heads > 16) {
+        set_err(ctx, "%s: q_heads must be a multiple of kv_heads with at most 16 query heads per kv head", who);
+        return FA_ERR_UNSUPPORTED_SHAPE;
+    }
+    if (!g->seq_lens && (g->seq_len < 0 || g->seq_len > g->s_max)) { set_err(ctx, "%s: seq_len must be in [0, s_max]", who); return FA_ERR_INVALID_ARG; }
+    if ((reinterpret_cast<uintptr_t>(g->q) & 3) || !aligned16(g->k_cache) || !aligned16(g->v_cache) || (reinterpret_cast<uintptr_t>(g->o) & 1)) {
+        set_err(ctx, "%s: k_cache/v_cache must be 16-byte aligned, q 4-byte aligned", who);
+        return FA_ERR_INVALID_ARG;
+    }
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) { set_err(ctx, "%s: cudaGetDevice: %s", who, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    if (cur != ctx->device) { set_err(ctx, "%s: the calling thread's current device differs from the context's device", who); return FA_ERR_INVALID_ARG; }
+    fa_sm100::DecodeArgs a{};
+    a.q = g->q; a.k_cache = g->k_cache; a.v_cache = g->v_cache; a.o = g->o; a.lse = static_cast<float*>(g->l_out);
+    a.seq_lens = g->seq_lens;
+    a.batch = g->batch; a.q_heads = g->q_heads; a.kv_heads = g->kv_heads; a.hd = g->head_dim;
+    a.s_max = g->s_max; a.seq_len = g->seq_len;
+    a.scale = g->scale; a.v_descale = (g->v_descale == 0.0f) ? 1.0f : g->v_descale;
+    a.scale_q_dev = g->scale_q_dev; a.scale_k_dev = g->scale_k_dev; a.scale_v_dev = g->scale_v_dev;
+    a.stream = reinterpret_cast<cudaStream_t>(g->stream);
+    const size_t ws_bytes = fa_sm100::decode_workspace_bytes(a.batch, a.kv_heads, a.hd, fa_sm100::decode_span(a));
+    void* ws = nullptr;
+    if (ws_bytes) {
+        e = cudaMallocFromPoolAsync(&ws, ws_bytes, ctx->pool, a.stream);
+        if (e != cudaSuccess) { set_err(ctx, "%s: workspace allocation: %s", who, cudaGetErrorString(e)); return e == cudaErrorMemoryAllocation ? FA_ERR_OOM : FA_ERR_CUDA; }
+    }
+    a.workspace = ws;
+    e = fa_sm100::launch_decode(a);
+    const cudaError_t fe = ws ? cudaFreeAsync(ws, a.stream) : cudaSuccess;  // stream-ordered: released after the kernels
+    if (e != cudaSuccess) { set_err(ctx, "%s: launch: %s", who, cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    if (fe != cudaSuccess) { set_err(ctx, "%s: workspace release: %s", who, cudaGetErrorString(fe)); return FA_ERR_CUDA; }
+    return FA_OK;
+}
+
 fa_status_t fa_device_status(fa_ctx_t* ctx) {
     if (!ctx) return FA_ERR_INVALID_ARG;
     const int code = fa_sm100::device_status();

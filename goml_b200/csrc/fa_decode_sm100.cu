@@ -1,0 +1,398 @@
+// fa_decode_sm100.cu — FP8 attention for one new token per sequence against an FP8 KV cache
+// (decode step), grouped-query heads, for NVIDIA B200 (sm_100a).
+//
+//   q        [B, Hq, D]          e4m3   (one token per sequence)
+//   k_cache  [B, Hkv, Smax, D]   e4m3   (the layout the prefill kernels read: BH = B*Hkv, S = Smax)
+//   v_cache  [B, Hkv, Smax, D]   e4m3
+//   o        [B, Hq, D]          fp16,  lse [B, Hq] fp32 (natural log, optional)
+//   seq_lens [B] int32 on the device (keys [0, seq_lens[b]) of sequence b are visible), or one length for all
+//
+// The step reads every cached key and value once and does 4*Hq*D FLOP per key: HBM-bound, so this is a
+// streaming kernel, not a tcgen05 one.  One CTA (4 warps) per (sequence, kv head, split of the key range); the
+// G = Hq/Hkv (<= 16) query heads that share a kv head form the 16 rows of the warp-level MMAs:
+//   S = Q K^T   mma.sync m16n8k32 e4m3 x e4m3 -> fp32, K fragments straight from a padded shared-memory copy
+//   P V         mma.sync m16n8k16 fp16 x fp16 -> fp32, P kept in fp16 (an e4m3 P costs 2.5e-2 relative error),
+//               V converted to fp16 on its way into shared memory and read with ldmatrix.trans
+// Each warp owns 16 of the 64 keys of a chunk and carries its own online-softmax state (m, l, O) over all chunks,
+// so the loop needs no cross-warp exchange; the four states are merged once at the end.  K and V chunks arrive
+// through a 3-stage cp.async ring (two chunks = 32 KB in flight per CTA, three CTAs per SM).  With more than one
+// split the partial states go to a workspace and a second kernel merges them.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "fa_fwd_sm100.h"
+
+namespace fa_sm100 {
+
+namespace {
+
+constexpr int CHUNK = 64;     // keys per step of a CTA
+constexpr int THREADS = 128;  // 4 warps x 16 keys
+constexpr int ROWS = 16;      // MMA rows = query heads of one kv head (padded)
+constexpr int STAGES = 3;     // cp.async ring depth (chunks)
+
+__device__ __forceinline__ void mma_e4m3_m16n8k32(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16_m16n8k16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(saddr));
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// 16 e4m3 codes -> 16 fp16 values (exact)
+__device__ __forceinline__ void e4m3x16_to_f16(const uint4 c, uint4& lo, uint4& hi) {
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    uint32_t h[8];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h[2 * k]) : "h"((uint16_t)(w[k] & 0xffffu)));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h[2 * k + 1]) : "h"((uint16_t)(w[k] >> 16)));
+    }
+    lo = make_uint4(h[0], h[1], h[2], h[3]);
+    hi = make_uint4(h[4], h[5], h[6], h[7]);
+}
+
+struct DecodeParams {
+    const uint8_t* q;
+    const uint8_t* k;
+    const uint8_t* v;
+    __half* o;
+    float* lse;
+    const int* seq_lens;
+    int batch, hq, hkv, group, s_max, seq_len;
+    float scale_log2, v_descale;
+    const float* sq;
+    const float* sk;
+    const float* sv;
+    int splits, chunks_per_split;
+    float* ws_o;   // [B*Hkv, splits, ROWS, D] un-normalised partial outputs
+    float* ws_ml;  // [B*Hkv, splits, ROWS, 2] (m in log2 units, l)
+};
+
+template <int D>
+struct Smem {
+    static constexpr int K_STRIDE = D + 16;          // bytes per key row of the e4m3 K copy (16 spreads rows over banks)
+    static constexpr int V_STRIDE = 2 * D + 16;      // bytes per key row of the fp16 V copy
+    static constexpr int K_BYTES = CHUNK * K_STRIDE;      // one ring stage of K
+    static constexpr int VRAW_BYTES = CHUNK * D;          // one ring stage of V codes (dense)
+    static constexpr int V_BYTES = CHUNK * V_STRIDE;      // the fp16 copy of the chunk being computed
+    static constexpr int OFF_VRAW = STAGES * K_BYTES;
+    static constexpr int OFF_V = OFF_VRAW + STAGES * VRAW_BYTES;
+    static constexpr int MERGE_BYTES = 4 * ROWS * (D + 2) * 4;   // four warps' (O, m, l) for the final merge
+    static constexpr int BYTES = (OFF_V + V_BYTES) > MERGE_BYTES ? (OFF_V + V_BYTES) : MERGE_BYTES;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParams p) {
+    using S = Smem<D>;
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* Vs = smem + S::OFF_V;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;              // MMA fragment coordinates
+    const int bh = blockIdx.x;                          // sequence * Hkv + kv head
+    const int b = bh / p.hkv, kvh = bh % p.hkv;
+    const int split = blockIdx.y;
+    const int seq_len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.s_max) : p.seq_len;
+    const int n_chunks = (seq_len + CHUNK - 1) / CHUNK;
+    const int c_begin = split * p.chunks_per_split;
+    const int c_end = min(n_chunks, c_begin + p.chunks_per_split);
+
+    float scale_log2 = p.scale_log2;
+    if (p.sq) scale_log2 *= __ldg(p.sq);
+    if (p.sk) scale_log2 *= __ldg(p.sk);
+
+    // Q fragments (A operand, 16 x D): rows g and g + 8 are query heads kvh*group + row of sequence b
+    constexpr int KSTEPS = D / 32;
+    uint32_t qa[KSTEPS][4];
+    {
+        const uint8_t* qb = p.q + ((size_t)b * p.hq + (size_t)kvh * p.group) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int row = g + 8 * r;
+                const bool live = row < p.group;
+                qa[ks][r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + ks * 32 + 4 * t) : 0u;
+                qa[ks][2 + r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + ks * 32 + 16 + 4 * t) : 0u;
+            }
+        }
+    }
+
+    // online-softmax state of this warp for rows g and g + 8
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float oacc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; n++) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
+
+    const uint8_t* kbase = p.k + (size_t)bh * p.s_max * D;
+    const uint8_t* vbase = p.v + (size_t)bh * p.s_max * D;
+    // a chunk is CHUNK * D contiguous bytes of K (and of V): PER_THREAD 16-byte pieces per thread
+    constexpr int PER_THREAD = CHUNK * D / 16 / THREADS;   // 4 (D = 128) or 2 (D = 64)
+    auto issue_chunk = [&](int c) {   // global -> ring stage (c - c_begin) % STAGES, one commit group per chunk
+        const int st = (c - c_begin) % STAGES;
+        const size_t off = (size_t)c * CHUNK * D;
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; i++) {
+            const int piece = i * THREADS + threadIdx.x;
+            const int key = piece / (D / 16), part = piece % (D / 16);
+            // keys past the end of this head's cache rows are not read (they would belong to the next head): zero-filled
+            const uint32_t nbytes = ((size_t)c * CHUNK + key < (size_t)p.s_max) ? 16u : 0u;
+            const uint32_t kd = smem_addr(smem + st * S::K_BYTES + key * S::K_STRIDE + part * 16);
+            const uint32_t vd = smem_addr(smem + S::OFF_VRAW + st * S::VRAW_BYTES + piece * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd), "l"(kbase + off + (size_t)piece * 16), "r"(nbytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd), "l"(vbase + off + (size_t)piece * 16), "r"(nbytes) : "memory");
+        }
+    };
+    auto commit = [&]() { asm volatile("cp.async.commit_group;" ::: "memory"); };
+    // V codes of the landed stage -> fp16 copy the P V fragments are read from
+    auto convert_v = [&](int st) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; i++) {
+            const int piece = i * THREADS + threadIdx.x;
+            const int key = piece / (D / 16), part = piece % (D / 16);
+            const uint4 codes = *reinterpret_cast<const uint4*>(smem + S::OFF_VRAW + st * S::VRAW_BYTES + piece * 16);
+            uint4 lo, hi;
+            e4m3x16_to_f16(codes, lo, hi);
+            uint4* vd = reinterpret_cast<uint4*>(Vs + key * S::V_STRIDE + part * 32);
+            vd[0] = lo;
+            vd[1] = hi;
+        }
+    };
+
+    // prologue: STAGES - 1 chunks in flight (empty groups keep the group count uniform)
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; i++) {
+        if (c_begin + i < c_end) issue_chunk(c_begin + i);
+        commit();
+    }
+    for (int c = c_begin; c < c_end; c++) {
+        const int st = (c - c_begin) % STAGES;
+        const uint8_t* Ks = smem + st * S::K_BYTES;
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // chunk c has landed (this thread's pieces)
+        __syncthreads();          // ... everyone's pieces; and all warps are done with the previous chunk's fragments
+        convert_v(st);
+        if (c + STAGES - 1 < c_end) issue_chunk(c + STAGES - 1);   // into the stage computed one iteration ago
+        commit();
+        __syncthreads();
+
+        // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+            const uint8_t* krow = Ks + (16 * warp + 8 * nt + g) * S::K_STRIDE;   // B fragment: key = column g of the n-tile
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 4 * t);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 16 + 4 * t);
+                mma_e4m3_m16n8k32(s[nt], qa[ks], b0, b1);
+            }
+        }
+        // scores: s[nt][0..1] = row g, keys 8nt + 2t, +1 ; s[nt][2..3] = row g + 8
+        const int key0 = c * CHUNK + 16 * warp;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = key0 + 8 * nt + 2 * t + (e & 1);
+                s[nt][e] = (key < seq_len) ? s[nt][e] * scale_log2 : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m[r], mx[r]);
+            corr[r] = (m[r] == -INFINITY) ? 0.f : ex2f(m[r] - m_new);   // m_new = -inf only if m is too
+            m[r] = m_new;
+        }
+        uint32_t pa[4];
+        float psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            float pv[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                pv[e] = (m[e >> 1] == -INFINITY) ? 0.f : ex2f(s[nt][e] - m[e >> 1]);
+                psum[e >> 1] += pv[e];
+            }
+            // A fragment of the 16 x 16 P tile: a0 = (row g, keys 2t..), a1 = (row g+8, ...), a2/a3 = keys + 8
+            pa[2 * nt] = pack_h2(pv[0], pv[1]);
+            pa[2 * nt + 1] = pack_h2(pv[2], pv[3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+            psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+            l[r] = l[r] * corr[r] + psum[r];
+        }
+        // ---- O = O * corr + P V over this warp's 16 keys
+        const uint32_t vrow = smem_addr(Vs + (16 * warp + (lane & 15)) * S::V_STRIDE);   // lanes 0..15 address the 16 key rows
+#pragma unroll
+        for (int n = 0; n < D / 8; n++) {
+            uint32_t b0, b1;
+            ldmatrix_x2_trans(b0, b1, vrow + n * 16);
+            oacc[n][0] *= corr[0];
+            oacc[n][1] *= corr[0];
+            oacc[n][2] *= corr[1];
+            oacc[n][3] *= corr[1];
+            mma_f16_m16n8k16(oacc[n], pa, b0, b1);
+        }
+    }
+
+    // ---- merge the four warps' states (shared memory reused)
+    __syncthreads();
+    float* mo = reinterpret_cast<float*>(smem);            // [4][ROWS][D]
+    float* mml = mo + 4 * ROWS * D;                        // [4][ROWS][2]
+#pragma unroll
+    for (int n = 0; n < D / 8; n++) {
+        float* base = mo + ((size_t)warp * ROWS) * D + n * 8 + 2 * t;
+        base[(size_t)g * D] = oacc[n][0];
+        base[(size_t)g * D + 1] = oacc[n][1];
+        base[(size_t)(g + 8) * D] = oacc[n][2];
+        base[(size_t)(g + 8) * D + 1] = oacc[n][3];
+    }
+    if (t == 0) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mml[(warp * ROWS + g + 8 * r) * 2] = m[r];
+            mml[(warp * ROWS + g + 8 * r) * 2 + 1] = l[r];
+        }
+    }
+    __syncthreads();
+    const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
+    for (int idx = threadIdx.x; idx < ROWS * D; idx += THREADS) {
+        const int row = idx / D, col = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, mml[(w * ROWS + row) * 2]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float mw = mml[(w * ROWS + row) * 2];
+            const float f = (mw == -INFINITY) ? 0.f : ex2f(mw - M);
+            L += mml[(w * ROWS + row) * 2 + 1] * f;
+            O += mo[((size_t)w * ROWS + row) * D + col] * f;
+        }
+        if (p.splits > 1) {
+            const size_t slot = ((size_t)bh * p.splits + split) * ROWS + row;
+            p.ws_o[slot * D + col] = O;
+            if (col == 0) {
+                p.ws_ml[slot * 2] = M;
+                p.ws_ml[slot * 2 + 1] = L;
+            }
+        } else if (row < p.group) {
+            const size_t orow = (size_t)b * p.hq + (size_t)kvh * p.group + row;
+            p.o[orow * D + col] = __float2half_rn(L > 0.f ? O * (vds / L) : 0.f);
+            if (col == 0 && p.lse) p.lse[orow] = (L > 0.f) ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+        }
+    }
+}
+
+// merges the splits of one (sequence, kv head): grid = B*Hkv, threads over ROWS x D
+template <int D>
+__global__ void __launch_bounds__(THREADS) fa_decode_combine_kernel(const DecodeParams p) {
+    const int bh = blockIdx.x;
+    const int b = bh / p.hkv, kvh = bh % p.hkv;
+    const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
+    for (int idx = threadIdx.x; idx < p.group * D; idx += THREADS) {
+        const int row = idx / D, col = idx % D;
+        float M = -INFINITY;
+        for (int s = 0; s < p.splits; s++) M = fmaxf(M, p.ws_ml[(((size_t)bh * p.splits + s) * ROWS + row) * 2]);
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < p.splits; s++) {
+            const size_t slot = ((size_t)bh * p.splits + s) * ROWS + row;
+            const float ms = p.ws_ml[slot * 2];
+            const float f = (ms == -INFINITY) ? 0.f : ex2f(ms - M);
+            L += p.ws_ml[slot * 2 + 1] * f;
+            O += p.ws_o[slot * D + col] * f;
+        }
+        const size_t orow = (size_t)b * p.hq + (size_t)kvh * p.group + row;
+        p.o[orow * D + col] = __float2half_rn(L > 0.f ? O * (vds / L) : 0.f);
+        if (col == 0 && p.lse) p.lse[orow] = (L > 0.f) ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+    }
+}
+
+int num_sms_of_current_device() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
+
+}  // namespace
+
+namespace {
+int decode_splits(int batch, int kv_heads, int span) {
+    const int chunks = (span + CHUNK - 1) / CHUNK;
+    const long long ctas = (long long)batch * kv_heads;
+    const int target = 4 * num_sms_of_current_device();   // a few CTAs per SM keep enough loads in flight
+    int splits = (int)((target + ctas - 1) / ctas);
+    if (splits > chunks) splits = chunks;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    return splits;
+}
+}  // namespace
+
+size_t decode_workspace_bytes(int batch, int kv_heads, int head_dim, int span) {
+    const int splits = decode_splits(batch, kv_heads, span);
+    if (splits <= 1) return 0;
+    return (size_t)batch * kv_heads * splits * ROWS * (head_dim + 2) * sizeof(float);
+}
+
+cudaError_t launch_decode(const DecodeArgs& a) {
+    DecodeParams p;
+    p.q = static_cast<const uint8_t*>(a.q);
+    p.k = static_cast<const uint8_t*>(a.k_cache);
+    p.v = static_cast<const uint8_t*>(a.v_cache);
+    p.o = static_cast<__half*>(a.o);
+    p.lse = a.lse;
+    p.seq_lens = a.seq_lens;
+    p.batch = a.batch; p.hq = a.q_heads; p.hkv = a.kv_heads; p.group = a.q_heads / a.kv_heads;
+    p.s_max = a.s_max; p.seq_len = a.seq_len;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.v_descale = a.v_descale;
+    p.sq = a.scale_q_dev; p.sk = a.scale_k_dev; p.sv = a.scale_v_dev;
+    const int span = decode_span(a);
+    p.splits = decode_splits(a.batch, a.kv_heads, span);
+    const int chunks = (span + CHUNK - 1) / CHUNK;
+    p.chunks_per_split = (chunks + p.splits - 1) / p.splits;
+    p.ws_o = static_cast<float*>(a.workspace);
+    p.ws_ml = p.ws_o ? p.ws_o + (size_t)a.batch * a.kv_heads * p.splits * ROWS * a.hd : nullptr;
+    if (p.splits > 1 && !a.workspace) return cudaErrorInvalidValue;
+    const dim3 grid((unsigned)(a.batch * a.kv_heads), (unsigned)p.splits);
+    if (a.hd == 128) {
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::BYTES);
+        if (e != cudaSuccess) return e;
+        fa_decode_kernel<128><<<grid, THREADS, Smem<128>::BYTES, a.stream>>>(p);
+        if (p.splits > 1) fa_decode_combine_kernel<128><<<grid.x, THREADS, 0, a.stream>>>(p);
+    } else {
+        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::BYTES);
+        if (e != cudaSuccess) return e;
+        fa_decode_kernel<64><<<grid, THREADS, Smem<64>::BYTES, a.stream>>>(p);
+        if (p.splits > 1) fa_decode_combine_kernel<64><<<grid.x, THREADS, 0, a.stream>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace fa_sm100

@@ -29,6 +29,27 @@ size_t workspace_bytes(int bh, int sl, int hd);
 // Launches on the calling thread's current device; asynchronous on a.stream.
 cudaError_t launch(const LaunchArgs& a);
 
+// ---- decode step: one new token per sequence against an FP8 KV cache, grouped-query heads (fa_decode_sm100.cu)
+struct DecodeArgs {
+    const void* q;         // [batch, q_heads, hd] e4m3
+    const void* k_cache;   // [batch, kv_heads, s_max, hd] e4m3
+    const void* v_cache;
+    void* o;               // [batch, q_heads, hd] fp16
+    float* lse;            // [batch, q_heads] or nullptr
+    const int* seq_lens;   // [batch] on the device, or nullptr: every sequence has seq_len keys
+    int batch, q_heads, kv_heads, hd, s_max, seq_len;
+    float scale, v_descale;
+    const float* scale_q_dev = nullptr;
+    const float* scale_k_dev = nullptr;
+    const float* scale_v_dev = nullptr;
+    void* workspace = nullptr;  // decode_workspace_bytes(...) bytes (0 when one split suffices)
+    cudaStream_t stream;
+};
+// Longest key range any sequence can have in this call (s_max with per-sequence lengths, else seq_len).
+inline int decode_span(const DecodeArgs& a) { return a.seq_lens ? a.s_max : a.seq_len; }
+size_t decode_workspace_bytes(int batch, int kv_heads, int head_dim, int span);
+cudaError_t launch_decode(const DecodeArgs& a);
+
 // Synchronises the device and returns (and clears) the first non-zero status
 // code a kernel recorded (a wait that ran out), 0 if none, -cudaError on failure.
 int device_status();

@@ -55,6 +55,19 @@ class ForwardArgs(C.Structure):
     ]
 
 
+class DecodeArgs(C.Structure):
+    """fa_decode_args_t (include/fa_sm120.h)."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("o", C.c_void_p), ("l_out", C.c_void_p),
+        ("seq_lens", C.c_void_p),
+        ("batch", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int),
+        ("s_max", C.c_int), ("seq_len", C.c_int),
+        ("scale", C.c_float), ("v_descale", C.c_float),
+        ("scale_q_dev", C.c_void_p), ("scale_k_dev", C.c_void_p), ("scale_v_dev", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 _lib_err = None
@@ -106,6 +119,8 @@ def FALoad():
                 lib.fa_forward_ex.argtypes = [p, C.POINTER(ForwardArgs)]
                 lib.fa_forward_noalloc.restype = i
                 lib.fa_forward_noalloc.argtypes = [C.POINTER(ForwardArgs), C.c_char_p, i]
+                lib.fa_decode.restype = i
+                lib.fa_decode.argtypes = [p, C.POINTER(DecodeArgs)]
                 lib.fa_device_status.restype = i
                 lib.fa_device_status.argtypes = [p]
                 _lib = lib
@@ -175,6 +190,18 @@ class FAContext:
         st = FALoad().fa_forward_ex(self.ptr, C.byref(a))
         if st != FA_OK:
             raise FAError("fa_forward_ex", st, self._msg())
+
+    def Decode(self, q, k_cache, v_cache, o, lOut, seq_lens, batch, q_heads, kv_heads, hd, s_max, seq_len, scale, v_descale=1.0,
+               scale_q_dev=0, scale_k_dev=0, scale_v_dev=0, stream=0) -> None:
+        """One new token per sequence against an e4m3 KV cache [batch, kv_heads, s_max, hd], grouped-query heads;
+        seq_lens: device pointer to batch int32 lengths, or 0 to use seq_len for every sequence."""
+        if not self.ptr:
+            raise FAError("FAContext.Decode: nil ctx", FA_ERR_INVALID_ARG)
+        a = DecodeArgs(q, k_cache, v_cache, o, lOut or None, seq_lens or None, batch, q_heads, kv_heads, hd, s_max, seq_len,
+                       scale, v_descale, scale_q_dev or None, scale_k_dev or None, scale_v_dev or None, stream or None)
+        st = FALoad().fa_decode(self.ptr, C.byref(a))
+        if st != FA_OK:
+            raise FAError("fa_decode", st, self._msg())
 
     def DeviceStatus(self) -> None:
         st = FALoad().fa_device_status(self.ptr)

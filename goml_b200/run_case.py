@@ -4,6 +4,7 @@
     python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
     python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
+    python -m goml_b200.run_case decode B HQ HKV S D ITERS     # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing
 
 torch only allocates the device buffers; every launch goes through the C ABI.
 """
@@ -45,6 +46,26 @@ def main(argv):
         for _ in range(iters):
             Q.QuantizeF32ToF8E4M3(x.data_ptr(), q.data_ptr(), s.data_ptr(), s.data_ptr() + 4, n, 0)
         torch.cuda.synchronize()
+    elif kind == "decode":
+        B, hq, hkv, S, D, iters = args
+        ctx = F.FACreate()
+        g = torch.Generator(device="cuda").manual_seed(0)
+        q = torch.randn(B, hq, D, device="cuda", generator=g).mul_(0.5).to(torch.float8_e4m3fn)
+        kc, vc = (torch.randn(B, hkv, S, D, device="cuda", generator=g).mul_(0.5).to(torch.float8_e4m3fn) for _ in range(2))
+        o = torch.empty(B, hq, D, dtype=torch.float16, device="cuda")
+        fn = lambda: ctx.Decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, 0, B, hq, hkv, D, S, S, 1 / math.sqrt(D))
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ctx.DeviceStatus()
+        us = e0.elapsed_time(e1) / iters * 1e3
+        nbytes = 2 * B * hkv * S * D
+        print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
     elif kind == "glue":
         B, S, d, H, Fh, iters = args
         T, hd, dev = B * S, d // H, "cuda"

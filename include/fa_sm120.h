@@ -163,6 +163,35 @@ FA_API fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* args);
  * (device address of the array, kernel attributes); make it before any stream capture. */
 FA_API fa_status_t fa_forward_noalloc(const fa_forward_args_t* args, char* err, int err_len);
 
+/* No counterpart in the reference (designed on paper there, runs/reports/F1_HF_INFERENCE_recon.md:55-68,163): the
+ * decode step of quantised inference — one new token per sequence attends to an FP8 KV cache, with grouped-query
+ * heads.  q [batch, q_heads, head_dim] e4m3; k_cache, v_cache [batch, kv_heads, s_max, head_dim] e4m3 (the layout
+ * fa_forward reads with batch_heads = batch * kv_heads and seq_len = s_max, so a cache filled during prefill is used
+ * as is); o [batch, q_heads, head_dim] fp16; l_out [batch, q_heads] fp32 natural-log LSE or NULL.  Query head h uses
+ * kv head h / (q_heads / kv_heads); q_heads / kv_heads must be an integer <= 16.  Sequence b sees keys
+ * [0, seq_lens[b]) (seq_lens: batch int32 values on the device, clamped to [0, s_max]) or, when seq_lens is NULL,
+ * keys [0, seq_len).  scale = softmax_scale * scale_Q * scale_K, v_descale and the optional device scale pointers as
+ * in fa_forward_ex.  A sequence with no visible key gets O = 0 and LSE = -inf.  HBM-bound: every cached key and value
+ * is read once. */
+typedef struct fa_decode_args {
+    const void* q;
+    const void* k_cache;
+    const void* v_cache;
+    void* o;
+    void* l_out;
+    const int* seq_lens;
+    int batch, q_heads, kv_heads, head_dim;
+    int s_max, seq_len;
+    float scale;
+    float v_descale;
+    const float* scale_q_dev;
+    const float* scale_k_dev;
+    const float* scale_v_dev;
+    fa_stream_t stream;
+} fa_decode_args_t;
+
+FA_API fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* args);
+
 /* Synchronises the context's device and reports whether any attention kernel
  * recorded a bounded-wait expiry since the last call: FA_OK, or FA_ERR_INTERNAL
  * with the code in fa_last_cuda_error. */

@@ -65,3 +65,28 @@ def swiglu_quantize(gu, F):
     y = (g / (f32(1.0) + e)) * u
     codes, scale, amax = O.quantize_f32(np.ascontiguousarray(y))
     return codes, scale, amax, y
+
+
+def decode_attention_f64(q, k_cache, v_cache, seq_lens, scale, v_descale=1.0):
+    """One query token per sequence against a KV cache, grouped-query heads, fp64 (the arithmetic of
+    internal/f64ref/attention.go:42-88 for a single query row: max-subtracted softmax over the visible keys,
+    all-masked row -> zeros; LSE as defined in libs/fa_sm120/include/fa_sm120.h:100-102).
+    q [B, Hq, D] e4m3 codes; k_cache, v_cache [B, Hkv, Smax, D] codes; seq_lens [B].  Returns (O [B, Hq, D], LSE [B, Hq])."""
+    qf, kf, vf = (O.e4m3_decode(np.asarray(t, np.uint8)).astype(np.float64) for t in (q, k_cache, v_cache))
+    B, Hq, D = qf.shape
+    Hkv = kf.shape[1]
+    group = Hq // Hkv
+    out = np.zeros((B, Hq, D))
+    lse = np.full((B, Hq), -np.inf)
+    for b in range(B):
+        n = int(seq_lens[b])
+        if n <= 0:
+            continue
+        for h in range(Hq):
+            kv = h // group
+            s = kf[b, kv, :n] @ qf[b, h] * scale
+            m = s.max()
+            p = np.exp(s - m)
+            out[b, h] = (p @ vf[b, kv, :n]) / p.sum() * v_descale
+            lse[b, h] = m + np.log(p.sum())
+    return out, lse
