@@ -14,8 +14,9 @@
 //   P V         mma.sync m16n8k16 fp16 x fp16 -> fp32, P kept in fp16 (an e4m3 P costs 2.5e-2 relative error),
 //               V converted to fp16 on its way into shared memory and read with ldmatrix.trans
 // Each warp owns 16 of the 64 keys of a chunk and carries its own online-softmax state (m, l, O) over all chunks,
-// so the loop needs no cross-warp exchange; the four states are merged once at the end.  K and V chunks arrive
-// through a 3-stage cp.async ring (two chunks = 32 KB in flight per CTA, three CTAs per SM).  With more than one
+// loading and converting its own keys, so the loop needs only warp-level synchronisation; the four states are merged
+// once at the end.  K and V chunks arrive through a 3-stage cp.async ring (two chunks = 32 KB in flight per CTA,
+// three CTAs per SM).  With more than one
 // split the partial states go to a workspace and a second kernel merges them.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -144,15 +145,18 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
 
     const uint8_t* kbase = p.k + (size_t)bh * p.s_max * D;
     const uint8_t* vbase = p.v + (size_t)bh * p.s_max * D;
-    // a chunk is CHUNK * D contiguous bytes of K (and of V): PER_THREAD 16-byte pieces per thread
-    constexpr int PER_THREAD = CHUNK * D / 16 / THREADS;   // 4 (D = 128) or 2 (D = 64)
+    // Each warp loads, converts and consumes its own 16 keys of every chunk (16 * D contiguous bytes of K and of V:
+    // PER_THREAD 16-byte pieces per lane), so the loop needs only warp-level synchronisation and the four warps of a
+    // CTA drift apart freely: their load latencies and MMA dependency stalls overlap instead of adding up.
+    constexpr int PER_THREAD = 16 * D / 16 / 32;   // 4 (D = 128) or 2 (D = 64)
     auto issue_chunk = [&](int c) {   // global -> ring stage (c - c_begin) % STAGES, one commit group per chunk
         const int st = (c - c_begin) % STAGES;
         const size_t off = (size_t)c * CHUNK * D;
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            const int piece = i * THREADS + threadIdx.x;
-            const int key = piece / (D / 16), part = piece % (D / 16);
+            const int wp = i * 32 + lane;                                  // piece within this warp's 16 keys
+            const int key = 16 * warp + wp / (D / 16), part = wp % (D / 16);
+            const int piece = key * (D / 16) + part;                       // piece within the chunk
             // keys past the end of this head's cache rows are not read (they would belong to the next head): zero-filled
             const uint32_t nbytes = ((size_t)c * CHUNK + key < (size_t)p.s_max) ? 16u : 0u;
             const uint32_t kd = smem_addr(smem + st * S::K_BYTES + key * S::K_STRIDE + part * 16);
@@ -166,8 +170,9 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     auto convert_v = [&](int st) {
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            const int piece = i * THREADS + threadIdx.x;
-            const int key = piece / (D / 16), part = piece % (D / 16);
+            const int wp = i * 32 + lane;
+            const int key = 16 * warp + wp / (D / 16), part = wp % (D / 16);
+            const int piece = key * (D / 16) + part;
             const uint4 codes = *reinterpret_cast<const uint4*>(smem + S::OFF_VRAW + st * S::VRAW_BYTES + piece * 16);
             uint4 lo, hi;
             e4m3x16_to_f16(codes, lo, hi);
@@ -186,25 +191,39 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     for (int c = c_begin; c < c_end; c++) {
         const int st = (c - c_begin) % STAGES;
         const uint8_t* Ks = smem + st * S::K_BYTES;
-        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // chunk c has landed (this thread's pieces)
-        __syncthreads();          // ... everyone's pieces; and all warps are done with the previous chunk's fragments
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // chunk c has landed (this lane's pieces)
+        __syncwarp();             // ... the whole warp's pieces; and every lane is done with the previous chunk's fragments
         convert_v(st);
         if (c + STAGES - 1 < c_end) issue_chunk(c + STAGES - 1);   // into the stage computed one iteration ago
         commit();
-        __syncthreads();
+        __syncwarp();
 
         // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys
+        // one accumulator per (n-tile, k-step): eight independent MMAs instead of two chains of four (the legacy
+        // mma.sync path has a 63-clock dependent-issue latency here), summed afterwards
         float s[2][4];
+        {
+            float part[2][KSTEPS][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-            const uint8_t* krow = Ks + (16 * warp + 8 * nt + g) * S::K_STRIDE;   // B fragment: key = column g of the n-tile
+            for (int nt = 0; nt < 2; nt++) {
+                const uint8_t* krow = Ks + (16 * warp + 8 * nt + g) * S::K_STRIDE;   // B fragment: key = column g of the n-tile
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 4 * t);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 16 + 4 * t);
-                mma_e4m3_m16n8k32(s[nt], qa[ks], b0, b1);
+                for (int ks = 0; ks < KSTEPS; ks++) {
+                    part[nt][ks][0] = part[nt][ks][1] = part[nt][ks][2] = part[nt][ks][3] = 0.f;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 4 * t);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 16 + 4 * t);
+                    mma_e4m3_m16n8k32(part[nt][ks], qa[ks], b0, b1);
+                }
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float acc = part[nt][0][e];
+#pragma unroll
+                    for (int ks = 1; ks < KSTEPS; ks++) acc += part[nt][ks][e];
+                    s[nt][e] = acc;
+                }
         }
         // scores: s[nt][0..1] = row g, keys 8nt + 2t, +1 ; s[nt][2..3] = row g + 8
         const int key0 = c * CHUNK + 16 * warp;
@@ -246,16 +265,19 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
             psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
             l[r] = l[r] * corr[r] + psum[r];
         }
-        // ---- O = O * corr + P V over this warp's 16 keys
+        // ---- O = O * corr + P V over this warp's 16 keys (the running maxima rarely move once a few chunks are in)
+        const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f);
         const uint32_t vrow = smem_addr(Vs + (16 * warp + (lane & 15)) * S::V_STRIDE);   // lanes 0..15 address the 16 key rows
 #pragma unroll
         for (int n = 0; n < D / 8; n++) {
             uint32_t b0, b1;
             ldmatrix_x2_trans(b0, b1, vrow + n * 16);
-            oacc[n][0] *= corr[0];
-            oacc[n][1] *= corr[0];
-            oacc[n][2] *= corr[1];
-            oacc[n][3] *= corr[1];
+            if (rescale) {
+                oacc[n][0] *= corr[0];
+                oacc[n][1] *= corr[0];
+                oacc[n][2] *= corr[1];
+                oacc[n][3] *= corr[1];
+            }
             mma_f16_m16n8k16(oacc[n], pa, b0, b1);
         }
     }
@@ -343,14 +365,16 @@ int num_sms_of_current_device() {
 
 namespace {
 int decode_splits(int batch, int kv_heads, int span) {
+    // Enough CTAs to fill the GPU once (three fit an SM) and no more: all of them resident at the same time, equal
+    // key ranges, so none waits for a second wave; with batch * kv_heads CTAs or more there is nothing to split.
     const int chunks = (span + CHUNK - 1) / CHUNK;
     const long long ctas = (long long)batch * kv_heads;
-    const int target = 4 * num_sms_of_current_device();   // a few CTAs per SM keep enough loads in flight
-    int splits = (int)((target + ctas - 1) / ctas);
+    const long long slots = 3LL * num_sms_of_current_device();
+    long long splits = slots / ctas;
     if (splits > chunks) splits = chunks;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
-    return splits;
+    return (int)splits;
 }
 }  // namespace
 

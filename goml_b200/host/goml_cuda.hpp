@@ -174,6 +174,7 @@ struct FaLib {
     decltype(&fa_forward) forward = nullptr;
     decltype(&fa_forward_train) forward_train = nullptr;
     decltype(&fa_forward_ex) forward_ex = nullptr;
+    decltype(&fa_decode) decode = nullptr;
     decltype(&fa_dispatch_select) dispatch = nullptr;
     decltype(&fa_kernel_name) kernel_name = nullptr;
     decltype(&fa_device_status) device_status = nullptr;
@@ -206,6 +207,7 @@ inline FaLib& fa_lib() {
         f.forward = sym<decltype(f.forward)>(f.lib, "fa_forward");
         f.forward_train = sym<decltype(f.forward_train)>(f.lib, "fa_forward_train");
         f.forward_ex = sym<decltype(f.forward_ex)>(f.lib, "fa_forward_ex");
+        f.decode = sym<decltype(f.decode)>(f.lib, "fa_decode");
         f.dispatch = sym<decltype(f.dispatch)>(f.lib, "fa_dispatch_select");
         f.kernel_name = sym<decltype(f.kernel_name)>(f.lib, "fa_kernel_name");
         f.device_status = sym<decltype(f.device_status)>(f.lib, "fa_device_status");
@@ -259,7 +261,13 @@ public:
         check("FAContext.ForwardEx");
         const FAStatus st = detail::fa_lib().forward_ex(ptr_, &a);
         if (st != FA_OK) fail("fa_forward_ex", st);
+    }    // One new token per sequence against an e4m3 KV cache, grouped-query heads (no counterpart in goml yet).
+    void Decode(const fa_decode_args_t& a) {
+        check("FAContext.Decode");
+        const FAStatus st = detail::fa_lib().decode(ptr_, &a);
+        if (st != FA_OK) fail("fa_decode", st);
     }
+
     void DeviceStatus() {
         const FAStatus st = detail::fa_lib().device_status(ptr_);
         if (st != FA_OK) fail("fa_device_status", st);
