@@ -143,26 +143,37 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
 #pragma unroll
     for (int n = 0; n < D / 8; n++) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.f;
 
-    const uint8_t* kbase = p.k + (size_t)bh * p.s_max * D;
-    const uint8_t* vbase = p.v + (size_t)bh * p.s_max * D;
     // Each warp loads, converts and consumes its own 16 keys of every chunk (16 * D contiguous bytes of K and of V:
     // PER_THREAD 16-byte pieces per lane), so the loop needs only warp-level synchronisation and the four warps of a
     // CTA drift apart freely: their load latencies and MMA dependency stalls overlap instead of adding up.
+    // The loop is issue-bound, so everything lane-constant is hoisted: 32-bit shared addresses, byte offsets of the
+    // lane's pieces and fragments; only the last chunk of a sequence is masked.
     constexpr int PER_THREAD = 16 * D / 16 / 32;   // 4 (D = 128) or 2 (D = 64)
+    constexpr int PARTS = D / 16;                   // 16-byte pieces per key row
+    const uint32_t sm = smem_addr(smem);
+    // piece i of this lane: key (16w + (32i + lane) / PARTS), part ((32i + lane) % PARTS); consecutive i are 32 pieces apart
+    const int key_l = 16 * warp + lane / PARTS, part_l = lane % PARTS;
+    const uint32_t k_dst = sm + key_l * S::K_STRIDE + part_l * 16;                      // + st * K_BYTES + i * (32 / PARTS) * K_STRIDE
+    const uint32_t vraw = sm + S::OFF_VRAW + (key_l * PARTS + part_l) * 16;              // + st * VRAW_BYTES + i * 512
+    const uint32_t v_dst = sm + S::OFF_V + key_l * S::V_STRIDE + part_l * 32;            // + i * (32 / PARTS) * V_STRIDE
+    const uint32_t k_frag = sm + (16 * warp + g) * S::K_STRIDE + 4 * t;                  // + st * K_BYTES + nt * 8 * K_STRIDE + ks * 32 (+16)
+    const uint32_t v_frag = sm + S::OFF_V + (16 * warp + (lane & 15)) * S::V_STRIDE;      // + n * 16
+    const size_t lane_goff = (size_t)(key_l * PARTS + part_l) * 16;                      // byte offset of piece 0 inside a chunk
+    const uint8_t* kg = p.k + (size_t)bh * p.s_max * D + lane_goff;
+    const uint8_t* vg = p.v + (size_t)bh * p.s_max * D + lane_goff;
     auto issue_chunk = [&](int c) {   // global -> ring stage (c - c_begin) % STAGES, one commit group per chunk
         const int st = (c - c_begin) % STAGES;
         const size_t off = (size_t)c * CHUNK * D;
+        // keys past the end of this head's cache rows are not read (they would belong to the next head): zero-filled
+        const bool whole = (c + 1) * CHUNK <= p.s_max;
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            const int wp = i * 32 + lane;                                  // piece within this warp's 16 keys
-            const int key = 16 * warp + wp / (D / 16), part = wp % (D / 16);
-            const int piece = key * (D / 16) + part;                       // piece within the chunk
-            // keys past the end of this head's cache rows are not read (they would belong to the next head): zero-filled
-            const uint32_t nbytes = ((size_t)c * CHUNK + key < (size_t)p.s_max) ? 16u : 0u;
-            const uint32_t kd = smem_addr(smem + st * S::K_BYTES + key * S::K_STRIDE + part * 16);
-            const uint32_t vd = smem_addr(smem + S::OFF_VRAW + st * S::VRAW_BYTES + piece * 16);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kd), "l"(kbase + off + (size_t)piece * 16), "r"(nbytes) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vd), "l"(vbase + off + (size_t)piece * 16), "r"(nbytes) : "memory");
+            const uint32_t nbytes = (whole || c * CHUNK + key_l + i * (32 / PARTS) < p.s_max) ? 16u : 0u;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(k_dst + st * S::K_BYTES + i * (32 / PARTS) * S::K_STRIDE),
+                         "l"(kg + off + i * 512), "r"(nbytes)
+                         : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vraw + st * S::VRAW_BYTES + i * 512), "l"(vg + off + i * 512), "r"(nbytes)
+                         : "memory");
         }
     };
     auto commit = [&]() { asm volatile("cp.async.commit_group;" ::: "memory"); };
@@ -170,15 +181,16 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     auto convert_v = [&](int st) {
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            const int wp = i * 32 + lane;
-            const int key = 16 * warp + wp / (D / 16), part = wp % (D / 16);
-            const int piece = key * (D / 16) + part;
-            const uint4 codes = *reinterpret_cast<const uint4*>(smem + S::OFF_VRAW + st * S::VRAW_BYTES + piece * 16);
-            uint4 lo, hi;
-            e4m3x16_to_f16(codes, lo, hi);
-            uint4* vd = reinterpret_cast<uint4*>(Vs + key * S::V_STRIDE + part * 32);
-            vd[0] = lo;
-            vd[1] = hi;
+            uint32_t w[4], h[8];
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(vraw + st * S::VRAW_BYTES + i * 512));
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\tcvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+                    : "=r"(h[2 * k]), "=r"(h[2 * k + 1])
+                    : "r"(w[k]));
+            const uint32_t dst = v_dst + i * (32 / PARTS) * S::V_STRIDE;
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
         }
     };
 
@@ -190,7 +202,6 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     }
     for (int c = c_begin; c < c_end; c++) {
         const int st = (c - c_begin) % STAGES;
-        const uint8_t* Ks = smem + st * S::K_BYTES;
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");   // chunk c has landed (this lane's pieces)
         __syncwarp();             // ... the whole warp's pieces; and every lane is done with the previous chunk's fragments
         convert_v(st);
@@ -198,20 +209,21 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
         commit();
         __syncwarp();
 
-        // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys
+        // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys.
         // one accumulator per (n-tile, k-step): eight independent MMAs instead of two chains of four (the legacy
         // mma.sync path has a 63-clock dependent-issue latency here), summed afterwards
         float s[2][4];
         {
             float part[2][KSTEPS][4];
+            const uint32_t kf = k_frag + st * S::K_BYTES;
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
-                const uint8_t* krow = Ks + (16 * warp + 8 * nt + g) * S::K_STRIDE;   // B fragment: key = column g of the n-tile
 #pragma unroll
                 for (int ks = 0; ks < KSTEPS; ks++) {
                     part[nt][ks][0] = part[nt][ks][1] = part[nt][ks][2] = part[nt][ks][3] = 0.f;
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 4 * t);
-                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 16 + 4 * t);
+                    uint32_t b0, b1;   // B fragment: key = column g of the n-tile, bytes 4t.. and 16 + 4t.. of the k-step
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32));
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32 + 16));
                     mma_e4m3_m16n8k32(part[nt][ks], qa[ks], b0, b1);
                 }
             }
@@ -222,20 +234,21 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
                     float acc = part[nt][0][e];
 #pragma unroll
                     for (int ks = 1; ks < KSTEPS; ks++) acc += part[nt][ks][e];
-                    s[nt][e] = acc;
+                    s[nt][e] = acc * scale_log2;
                 }
         }
         // scores: s[nt][0..1] = row g, keys 8nt + 2t, +1 ; s[nt][2..3] = row g + 8
-        const int key0 = c * CHUNK + 16 * warp;
-        float mx[2] = {-INFINITY, -INFINITY};
+        if ((c + 1) * CHUNK > seq_len) {   // only the last chunk of a sequence has keys past its end
+            const int key0 = c * CHUNK + 16 * warp;
 #pragma unroll
-        for (int nt = 0; nt < 2; nt++)
+            for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int key = key0 + 8 * nt + 2 * t + (e & 1);
-                s[nt][e] = (key < seq_len) ? s[nt][e] * scale_log2 : -INFINITY;
-                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
-            }
+                for (int e = 0; e < 4; e++)
+                    if (key0 + 8 * nt + 2 * t + (e & 1) >= seq_len) s[nt][e] = -INFINITY;
+        }
+        float mx[2];
+        mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; r++) {
@@ -267,11 +280,10 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
         }
         // ---- O = O * corr + P V over this warp's 16 keys (the running maxima rarely move once a few chunks are in)
         const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f);
-        const uint32_t vrow = smem_addr(Vs + (16 * warp + (lane & 15)) * S::V_STRIDE);   // lanes 0..15 address the 16 key rows
 #pragma unroll
         for (int n = 0; n < D / 8; n++) {
             uint32_t b0, b1;
-            ldmatrix_x2_trans(b0, b1, vrow + n * 16);
+            ldmatrix_x2_trans(b0, b1, v_frag + n * 16);
             if (rescale) {
                 oacc[n][0] *= corr[0];
                 oacc[n][1] *= corr[0];
