@@ -57,19 +57,6 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-// 16 e4m3 codes -> 16 fp16 values (exact)
-__device__ __forceinline__ void e4m3x16_to_f16(const uint4 c, uint4& lo, uint4& hi) {
-    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
-    uint32_t h[8];
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h[2 * k]) : "h"((uint16_t)(w[k] & 0xffffu)));
-        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h[2 * k + 1]) : "h"((uint16_t)(w[k] >> 16)));
-    }
-    lo = make_uint4(h[0], h[1], h[2], h[3]);
-    hi = make_uint4(h[4], h[5], h[6], h[7]);
-}
-
 struct DecodeParams {
     const uint8_t* q;
     const uint8_t* k;
@@ -155,7 +142,6 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     const int key_l = 16 * warp + lane / PARTS, part_l = lane % PARTS;
     const uint32_t k_dst = sm + key_l * S::K_STRIDE + part_l * 16;                      // + st * K_BYTES + i * (32 / PARTS) * K_STRIDE
     const uint32_t vraw = sm + S::OFF_VRAW + (key_l * PARTS + part_l) * 16;              // + st * VRAW_BYTES + i * 512
-    const uint32_t v_dst = sm + S::OFF_V + key_l * S::V_STRIDE + part_l * 32;            // + i * (32 / PARTS) * V_STRIDE
     const uint32_t k_frag = sm + (16 * warp + g) * S::K_STRIDE + 4 * t;                  // + st * K_BYTES + nt * 8 * K_STRIDE + ks * 32 (+16)
     const uint32_t v_frag = sm + S::OFF_V + (16 * warp + (lane & 15)) * S::V_STRIDE;      // + n * 16
     const size_t lane_goff = (size_t)(key_l * PARTS + part_l) * 16;                      // byte offset of piece 0 inside a chunk
@@ -179,18 +165,23 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     auto commit = [&]() { asm volatile("cp.async.commit_group;" ::: "memory"); };
     // V codes of the landed stage -> fp16 copy the P V fragments are read from
     auto convert_v = [&](int st) {
+        // lane j of the 8 (4) lanes of a key row converts codes [8j, 8j+8) and [D/2 + 8j, D/2 + 8j + 8): each of its two
+        // 16-byte stores then lands next to its neighbours' (bank-conflict free), unlike a 32-byte run per lane
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            uint32_t w[4], h[8];
-            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(vraw + st * S::VRAW_BYTES + i * 512));
+            const uint32_t src = sm + S::OFF_VRAW + st * S::VRAW_BYTES + (key_l + i * (32 / PARTS)) * D + part_l * 8;
+            const uint32_t dst = sm + S::OFF_V + (key_l + i * (32 / PARTS)) * S::V_STRIDE + part_l * 16;
 #pragma unroll
-            for (int k = 0; k < 4; k++)
-                asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\tcvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
-                    : "=r"(h[2 * k]), "=r"(h[2 * k + 1])
-                    : "r"(w[k]));
-            const uint32_t dst = v_dst + i * (32 / PARTS) * S::V_STRIDE;
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+            for (int hlf = 0; hlf < 2; hlf++) {
+                uint32_t w[2], h[4];
+                asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(src + hlf * (D / 2)));
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+                    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\tcvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+                        : "=r"(h[2 * k]), "=r"(h[2 * k + 1])
+                        : "r"(w[k]));
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst + hlf * D), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+            }
         }
     };
 
