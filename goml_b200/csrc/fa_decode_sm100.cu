@@ -34,10 +34,11 @@ constexpr int THREADS = 128;  // 4 warps x 16 keys
 constexpr int ROWS = 16;      // MMA rows = query heads of one kv head (padded)
 constexpr int STAGES = 3;     // cp.async ring depth (chunks)
 
-__device__ __forceinline__ void mma_e4m3_m16n8k32(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D = A B with a zero accumulator input (no registers to clear first)
+__device__ __forceinline__ void mma_e4m3_m16n8k32_zero(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ void mma_f16_m16n8k16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -211,11 +212,10 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
             for (int nt = 0; nt < 2; nt++) {
 #pragma unroll
                 for (int ks = 0; ks < KSTEPS; ks++) {
-                    part[nt][ks][0] = part[nt][ks][1] = part[nt][ks][2] = part[nt][ks][3] = 0.f;
                     uint32_t b0, b1;   // B fragment: key = column g of the n-tile, bytes 4t.. and 16 + 4t.. of the k-step
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32));
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32 + 16));
-                    mma_e4m3_m16n8k32(part[nt][ks], qa[ks], b0, b1);
+                    mma_e4m3_m16n8k32_zero(part[nt][ks], qa[ks], b0, b1);
                 }
             }
 #pragma unroll
