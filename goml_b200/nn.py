@@ -177,10 +177,23 @@ class FP8DecoderBlock:
 def _main():
     """Times the full-size block config: d_model 4096, 32 heads x 128, SwiGLU hidden 11008, B=8 x S=2048
     tokens, random-init weights N(0, 0.02), embeddings N(0, 1) — the whole block and its FP8 kernels alone."""
+    import os
     import sys
     B, S, d, H, Fh = 8, 2048, 4096, 32, 11008
     if len(sys.argv) > 1:
         B = int(sys.argv[1])
+    # Under torchrun the block is sharded by rows on sequence boundaries (the M-tile partition of the GEMMs and the
+    # batch*head partition of the attention coincide there): weights replicated, no collective on the data path;
+    # torch.distributed is used for the barrier and the max-over-ranks of the timing only.
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        from .multi_gpu import shard_rows
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        lo, hi = shard_rows(B * S, world, rank, tile=S)      # whole sequences per rank
+        B_global, B = B, (hi - lo) // S
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(4)
     rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device=dev) * std
@@ -199,6 +212,17 @@ def _main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters
 
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([timed(lambda: blk(x, B, S), iters=10)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            fl = 2.0 * B_global * S * d * (3 * d + d + 3 * Fh) + 2.0 * B_global * H * S * S * (d // H)
+            print(f"block B={B_global} S={S} d={d} H={H} F={Fh} over {world} GPUs ({B} sequences per GPU, no collective): "
+                  f"{t.item():.3f} ms (max over ranks) = {fl / t.item() / 1e9:.0f} TFLOPS whole job")
+        blk.close()
+        dist.destroy_process_group()
+        return
     total = timed(lambda: blk(x, B, S))
     blk.fused = False
     total_unfused = timed(lambda: blk(x, B, S))
