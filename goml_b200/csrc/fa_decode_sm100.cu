@@ -15,8 +15,9 @@
 //               V converted to fp16 on its way into shared memory and read with ldmatrix.trans
 // Each warp owns 16 of the 64 keys of a chunk and carries its own online-softmax state (m, l, O) over all chunks,
 // loading and converting its own keys, so the loop needs only warp-level synchronisation; the four states are merged
-// once at the end.  K and V chunks arrive through a 3-stage cp.async ring (two chunks = 32 KB in flight per CTA,
-// three CTAs per SM).  With more than one
+// once at the end.  K and V chunks arrive through a 2-stage cp.async ring (one chunk = 16 KB in flight per CTA,
+// four CTAs = 16 warps per SM: the loop is bound by instruction issue and dependency stalls, which more warps hide
+// better than a deeper ring).  With more than one
 // split the partial states go to a workspace and a second kernel merges them.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,7 +33,14 @@ namespace {
 constexpr int CHUNK = 64;     // keys per step of a CTA
 constexpr int THREADS = 128;  // 4 warps x 16 keys
 constexpr int ROWS = 16;      // MMA rows = query heads of one kv head (padded)
-constexpr int STAGES = 3;     // cp.async ring depth (chunks)
+#ifndef FA_DECODE_STAGES
+#define FA_DECODE_STAGES 2
+#endif
+#ifndef FA_DECODE_CTAS
+#define FA_DECODE_CTAS 4
+#endif
+constexpr int STAGES = FA_DECODE_STAGES;     // cp.async ring depth (chunks)
+constexpr int CTAS_PER_SM = FA_DECODE_CTAS;  // resident CTAs the register budget is set for
 
 // D = A B with a zero accumulator input (no registers to clear first)
 __device__ __forceinline__ void mma_e4m3_m16n8k32_zero(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -45,8 +53,8 @@ __device__ __forceinline__ void mma_f16_m16n8k16(float* c, const uint32_t* a, ui
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t saddr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(saddr));
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(saddr));
 }
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ float ex2f(float x) {
@@ -89,7 +97,7 @@ struct Smem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM) fa_decode_kernel(const DecodeParams p) {
     using S = Smem<D>;
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* Vs = smem + S::OFF_V;
@@ -108,7 +116,11 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     if (p.sq) scale_log2 *= __ldg(p.sq);
     if (p.sk) scale_log2 *= __ldg(p.sk);
 
-    // Q fragments (A operand, 16 x D): rows g and g + 8 are query heads kvh*group + row of sequence b
+    // Q fragments (A operand, 16 x D): rows g and g + 8 are query heads kvh*group + row of sequence b.
+    // The contraction order over d is free, so the MMA's k index is fed a permutation of d that makes every lane's
+    // share of a key row contiguous: lane t supplies d = (D/4)*t + 8*ks + {0..3} as k = 4t + {0..3} and
+    // d = (D/4)*t + 8*ks + 4 + {0..3} as k = 16 + 4t + {0..3} of k-step ks, for Q (here) and K (below) alike; its K
+    // fragments of all k-steps are then D/4 contiguous bytes (two 128-bit shared loads for D = 128).
     constexpr int KSTEPS = D / 32;
     uint32_t qa[KSTEPS][4];
     {
@@ -119,8 +131,8 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
             for (int r = 0; r < 2; r++) {
                 const int row = g + 8 * r;
                 const bool live = row < p.group;
-                qa[ks][r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + ks * 32 + 4 * t) : 0u;
-                qa[ks][2 + r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + ks * 32 + 16 + 4 * t) : 0u;
+                qa[ks][r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + (D / 4) * t + 8 * ks) : 0u;
+                qa[ks][2 + r] = live ? *reinterpret_cast<const uint32_t*>(qb + (size_t)row * D + (D / 4) * t + 8 * ks + 4) : 0u;
             }
         }
     }
@@ -143,8 +155,9 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
     const int key_l = 16 * warp + lane / PARTS, part_l = lane % PARTS;
     const uint32_t k_dst = sm + key_l * S::K_STRIDE + part_l * 16;                      // + st * K_BYTES + i * (32 / PARTS) * K_STRIDE
     const uint32_t vraw = sm + S::OFF_VRAW + (key_l * PARTS + part_l) * 16;              // + st * VRAW_BYTES + i * 512
-    const uint32_t k_frag = sm + (16 * warp + g) * S::K_STRIDE + 4 * t;                  // + st * K_BYTES + nt * 8 * K_STRIDE + ks * 32 (+16)
-    const uint32_t v_frag = sm + S::OFF_V + (16 * warp + (lane & 15)) * S::V_STRIDE;      // + n * 16
+    const uint32_t k_frag = sm + (16 * warp + g) * S::K_STRIDE + (D / 4) * t;            // + st * K_BYTES + nt * 8 * K_STRIDE: D/4 bytes = all k-steps
+    // ldmatrix.x4: lanes 0-15 address the 16 key rows at d-tile n, lanes 16-31 the same rows at d-tile n + 1
+    const uint32_t v_frag = sm + S::OFF_V + (16 * warp + (lane & 15)) * S::V_STRIDE + (lane >> 4) * 16;   // + n * 16
     const size_t lane_goff = (size_t)(key_l * PARTS + part_l) * 16;                      // byte offset of piece 0 inside a chunk
     const uint8_t* kg = p.k + (size_t)bh * p.s_max * D + lane_goff;
     const uint8_t* vg = p.v + (size_t)bh * p.s_max * D + lane_goff;
@@ -210,13 +223,15 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
             const uint32_t kf = k_frag + st * S::K_BYTES;
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
+                // B fragments of every k-step: key = column g of the n-tile, this lane's D/4 contiguous bytes of its row
+                uint32_t kw[D / 16];
 #pragma unroll
-                for (int ks = 0; ks < KSTEPS; ks++) {
-                    uint32_t b0, b1;   // B fragment: key = column g of the n-tile, bytes 4t.. and 16 + 4t.. of the k-step
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32));
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(kf + nt * 8 * S::K_STRIDE + ks * 32 + 16));
-                    mma_e4m3_m16n8k32_zero(part[nt][ks], qa[ks], b0, b1);
-                }
+                for (int v = 0; v < D / 64; v++)
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(kw[4 * v]), "=r"(kw[4 * v + 1]), "=r"(kw[4 * v + 2]), "=r"(kw[4 * v + 3])
+                                 : "r"(kf + nt * 8 * S::K_STRIDE + 16 * v));
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ks++) mma_e4m3_m16n8k32_zero(part[nt][ks], qa[ks], kw[2 * ks], kw[2 * ks + 1]);
             }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
@@ -272,16 +287,20 @@ __global__ void __launch_bounds__(THREADS, 3) fa_decode_kernel(const DecodeParam
         // ---- O = O * corr + P V over this warp's 16 keys (the running maxima rarely move once a few chunks are in)
         const bool rescale = !__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f);
 #pragma unroll
-        for (int n = 0; n < D / 8; n++) {
-            uint32_t b0, b1;
-            ldmatrix_x2_trans(b0, b1, v_frag + n * 16);
+        for (int n = 0; n < D / 8; n += 2) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, v_frag + n * 16);
             if (rescale) {
-                oacc[n][0] *= corr[0];
-                oacc[n][1] *= corr[0];
-                oacc[n][2] *= corr[1];
-                oacc[n][3] *= corr[1];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    oacc[n + h][0] *= corr[0];
+                    oacc[n + h][1] *= corr[0];
+                    oacc[n + h][2] *= corr[1];
+                    oacc[n + h][3] *= corr[1];
+                }
             }
             mma_f16_m16n8k16(oacc[n], pa, b0, b1);
+            mma_f16_m16n8k16(oacc[n + 1], pa, b2, b3);
         }
     }
 
@@ -368,11 +387,11 @@ int num_sms_of_current_device() {
 
 namespace {
 int decode_splits(int batch, int kv_heads, int span) {
-    // Enough CTAs to fill the GPU once (three fit an SM) and no more: all of them resident at the same time, equal
+    // Enough CTAs to fill the GPU once (CTAS_PER_SM fit an SM) and no more: all of them resident at the same time, equal
     // key ranges, so none waits for a second wave; with batch * kv_heads CTAs or more there is nothing to split.
     const int chunks = (span + CHUNK - 1) / CHUNK;
     const long long ctas = (long long)batch * kv_heads;
-    const long long slots = 3LL * num_sms_of_current_device();
+    const long long slots = (long long)CTAS_PER_SM * num_sms_of_current_device();
     long long splits = slots / ctas;
     if (splits > chunks) splits = chunks;
     if (splits > 64) splits = 64;
