@@ -34,9 +34,9 @@ METRIC = "FP8 attn-fwd & FP8 GEMM TFLOPS/GPU (hd128 S=8192; 8192^3) at 1/2/4/8 B
 ATT = dict(bh=128, sl=8192, hd=128, causal=0)
 GEMM = dict(M=8192, N=8192, K=8192)
 NOMINAL_FP8_TFLOPS = 4500.0
-FALLBACK_BF16_TFLOPS = 1590.0  # profiling-recipe fallback when MEASURED_PEAKS.json is absent
+FALLBACK_BF16_TFLOPS = 1590.0  # fallback when the measured-peaks file is absent
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel at the bench
-# shape, from the ncu capture summarised in profiles/fa_fwd_hd128_bh32_s8192.md
+# shape, from an ncu capture of a quarter of it (BH=32, S=8192, D=128; 134.27 MB read + 41.31 MB written)
 ATTN_DRAM_TRAFFIC_BYTES = 4 * (134.27e6 + 41.31e6)  # 4 x the BH=32 capture (traffic grows with the number of heads)
 
 
