@@ -357,7 +357,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             o.y = pack_out(__uint_as_float(acc[8 * v + 2]) * alpha, __uint_as_float(acc[8 * v + 3]) * alpha, p.out_bf16);
                             o.z = pack_out(__uint_as_float(acc[8 * v + 4]) * alpha, __uint_as_float(acc[8 * v + 5]) * alpha, p.out_bf16);
                             o.w = pack_out(__uint_as_float(acc[8 * v + 6]) * alpha, __uint_as_float(acc[8 * v + 7]) * alpha, p.out_bf16);
-                            dst[v] = o;
+                            __stcs(dst + v, o);  // streaming store: C is not read again, keep A and B panels in L2
                         }
                     } else {
 #pragma unroll
