@@ -5,6 +5,7 @@
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
     python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
     python -m goml_b200.run_case decode B HQ HKV S D ITERS     # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing
+    python -m goml_b200.run_case block B S D H F ITERS         # one fused FP8 decoder block (goml_b200.nn), random-init weights
 
 torch only allocates the device buffers; every launch goes through the C ABI.
 """
@@ -46,6 +47,25 @@ def main(argv):
         for _ in range(iters):
             Q.QuantizeF32ToF8E4M3(x.data_ptr(), q.data_ptr(), s.data_ptr(), s.data_ptr() + 4, n, 0)
         torch.cuda.synchronize()
+    elif kind == "block":
+        from . import nn
+        B, S, d, H, Fh, iters = args
+        g = torch.Generator(device="cuda").manual_seed(4)
+        rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device="cuda") * std
+        blk = nn.FP8DecoderBlock(d, H, Fh, rn(3 * d, d), rn(d, d), rn(2 * Fh, d), rn(d, Fh), torch.ones(d, device="cuda"), torch.ones(d, device="cuda"))
+        x = rn(B * S, d, std=1.0)
+        blk(x, B, S)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            y = blk(x, B, S)
+        e1.record()
+        torch.cuda.synchronize()
+        blk.fa.DeviceStatus()
+        assert G.device_status() == 0 and bool(torch.isfinite(y).all())
+        print(f"block B={B} S={S} d={d} H={H} F={Fh}: {e0.elapsed_time(e1) / iters:.3f} ms per block")
+        blk.close()
     elif kind == "decode":
         B, hq, hkv, S, D, iters = args
         ctx = F.FACreate()
