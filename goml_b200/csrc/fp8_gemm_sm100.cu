@@ -76,6 +76,9 @@ struct GemmParams {
     void* H;
     int F;
     float* amax;
+    // e4m3-output mode: D8[M,N] = e4m3(scale_d * v), v = alpha * A.B^T rounded to fp32, and max|v| reduced into *amax
+    uint8_t* D8;
+    const float* scale_d;
     int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
     int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
@@ -118,6 +121,14 @@ __device__ __forceinline__ uint32_t pack_out(float a, float b, int bf16) {
     }
     __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// four fp32 -> four e4m3 codes (round to nearest even, saturate to +-448, NaN -> 0x7f), a in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
 template <int BN>
@@ -243,6 +254,8 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (p.scale_b) alpha *= __ldg(p.scale_b);
         const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
         const bool xvec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.X) & 15) == 0);
+        const bool dvec_ok = (p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.D8) & 15) == 0);
+        const float scale_d = (p.D8 && p.scale_d) ? __ldg(p.scale_d) : 1.0f;
         uint32_t tphase[2] = {0, 0};
         int buf = 0;
         int sbuf = 0;  // staging box in use (accumulate mode)
@@ -255,11 +268,11 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const int row = tm * BM + row_in_tile;
             const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
+            float tmax = 0.f;  // running max of this thread's row (SwiGLU and e4m3-output modes)
             if (BN == 256 && p.H) {
                 // gate columns [0,128) and up columns [128,256) of the accumulator -> 128 activations per row
                 uint16_t* hrow = reinterpret_cast<uint16_t*>(p.H) + (size_t)row * p.F;
                 const bool hvec_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.H) & 15) == 0);
-                float tmax = 0.f;
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     const int col0 = (n0 >> 1) + c * 32;   // activation column of this chunk
@@ -297,10 +310,6 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         }
                     }
                 }
-                // rows >= M and columns >= F hold zeros (zero-filled operand rows): they never raise the maximum
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
-                if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
             } else
 #pragma unroll 1
             for (int c = 0; c < bn / 32; c++) {
@@ -330,6 +339,36 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         tma_store_commit();
                     }
                     sbuf ^= 1;
+                } else if (p.D8) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        v[j] = __uint_as_float(acc[j]) * alpha;
+                        tmax = fmaxf(tmax, fabsf(v[j]));
+                        v[j] *= scale_d;
+                    }
+                    if (row < p.M) {
+                        uint8_t* drow = p.D8 + (size_t)row * p.N + col0;
+                        if (dvec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                uint4 o;
+                                o.x = pack_e4m3x4(v[16 * h + 0], v[16 * h + 1], v[16 * h + 2], v[16 * h + 3]);
+                                o.y = pack_e4m3x4(v[16 * h + 4], v[16 * h + 5], v[16 * h + 6], v[16 * h + 7]);
+                                o.z = pack_e4m3x4(v[16 * h + 8], v[16 * h + 9], v[16 * h + 10], v[16 * h + 11]);
+                                o.w = pack_e4m3x4(v[16 * h + 12], v[16 * h + 13], v[16 * h + 14], v[16 * h + 15]);
+                                __stcs(reinterpret_cast<uint4*>(drow) + h, o);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const uint32_t w = pack_e4m3x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+#pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    if (col0 + j + e < p.N) drow[j + e] = (uint8_t)(w >> (8 * e));
+                            }
+                        }
+                    }
                 } else if (row < p.M && p.X) {
                     float* xrow = p.X + (size_t)row * p.N + col0;
                     if (xvec_ok && col0 + 32 <= p.N) {
@@ -377,6 +416,12 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             buf ^= 1;
+            if (p.amax) {
+                // rows >= M and columns past the matrix hold zeros (zero-filled operand rows): they never raise the maximum
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+                if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
+            }
         }
         if (p.X && p.x_tma && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
@@ -409,10 +454,11 @@ constexpr int MAX_DEVICES = 64;
 DeviceState g_dev[MAX_DEVICES];
 
 int launch(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* sa, const float* sb,
-           int out_bf16, cudaStream_t stream, float* X = nullptr, void* H = nullptr, int F = 0, float* amax = nullptr) {
+           int out_bf16, cudaStream_t stream, float* X = nullptr, void* H = nullptr, int F = 0, float* amax = nullptr,
+           uint8_t* D8 = nullptr, const float* scale_d = nullptr) {
     if (M < 0 || N < 0 || K < 0) return (int)cudaErrorInvalidValue;
     if (M == 0 || N == 0) return 0;
-    if (!A || !B || (!C && !X && !H)) return (int)cudaErrorInvalidValue;
+    if (!A || !B || (!C && !X && !H && !D8)) return (int)cudaErrorInvalidValue;
     if (H && (!amax || F <= 0 || N != 2 * ((F + 127) / 128) * 128 || (reinterpret_cast<uintptr_t>(H) & 1))) return (int)cudaErrorInvalidValue;
     if (K == 0 || (K % 16) != 0) return (int)cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
@@ -459,6 +505,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
     p.X = X;
     p.H = H; p.F = F; p.amax = amax;
+    p.D8 = D8; p.scale_d = scale_d;
     p.x_tma = (X && (N % 4) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) ? 1 : 0;
     p.m_tiles = (int)m_tiles;
     p.n_tiles = (N + bn - 1) / bn;
@@ -525,6 +572,17 @@ int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleave
     if (e != cudaSuccess) return (int)e;
     const int n = 2 * ((F + 127) / 128) * 128;
     return launch(M, n, K, A, B_interleaved, nullptr, alpha, scale_a, scale_b, 1, (cudaStream_t)stream, nullptr, H, F, amax_out);
+}
+
+int fp8_gemm_fp8out(int M, int N, int K, const void* A, const void* B, void* D, float alpha, const float* scale_a,
+                    const float* scale_b, const float* scale_d, float* amax_d, void* stream) {
+    if (!D) return (int)cudaErrorInvalidValue;
+    if (amax_d) {
+        cudaError_t e = cudaMemsetAsync(amax_d, 0, sizeof(float), (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch(M, N, K, A, B, nullptr, alpha, scale_a, scale_b, 0, (cudaStream_t)stream, nullptr, nullptr, 0, amax_d,
+                  reinterpret_cast<uint8_t*>(D), scale_d);
 }
 
 int fp8_gemm_device_status(void) {

@@ -46,6 +46,8 @@ def _init():
                 lib.fp8_gemm_accumulate_f32.argtypes = [i, i, i, p, p, p, f, p, p, p]
                 lib.fp8_gemm_swiglu.restype = i
                 lib.fp8_gemm_swiglu.argtypes = [i, i, i, p, p, p, f, p, p, p, p]
+                lib.fp8_gemm_fp8out.restype = i
+                lib.fp8_gemm_fp8out.argtypes = [i, i, i, p, p, p, f, p, p, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
                 lib.fp8_gemm_version.restype = C.c_char_p
                 _state["lib"] = lib
@@ -94,6 +96,15 @@ def FP8GEMMSwiGLU(M, F, K, A, B_interleaved, H, alpha=1.0, scale_a=0, scale_b=0,
     rc = _init().fp8_gemm_swiglu(M, F, K, A, B_interleaved, H, alpha, scale_a or None, scale_b or None, amax_out, stream or None)
     if rc != 0:
         raise FP8GEMMError(f"fp8_gemm_swiglu: CUDA error {rc}")
+
+
+def FP8GEMMFP8Out(M, N, K, A, B, D, alpha=1.0, scale_a=0, scale_b=0, scale_d=0, amax_d=0, stream=0) -> None:
+    """D (e4m3 [M, N]) = e4m3((*scale_d) * v), v = alpha * sa * sb * A x B^T; max|v| -> *amax_d (0 = not wanted).
+    The delayed-scaling epilogue of fp8_matmul_fp8out (libs1/cublas_lt_wrapper_v3.c:220-229)."""
+    rc = _init().fp8_gemm_fp8out(M, N, K, A, B, D, alpha, scale_a or None, scale_b or None, scale_d or None,
+                                 amax_d or None, stream or None)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_fp8out: CUDA error {rc}")
 
 
 def interleave_gate_up(w_gate_up, F: int):

@@ -93,6 +93,7 @@ struct GemmLib {
     int (*scaled)(int, int, int, const void*, const void*, void*, float, const float*, const float*, int, void*) = nullptr;
     int (*accumulate)(int, int, int, const void*, const void*, float*, float, const float*, const float*, void*) = nullptr;
     int (*swiglu)(int, int, int, const void*, const void*, void*, float, const float*, const float*, float*, void*) = nullptr;
+    int (*fp8out)(int, int, int, const void*, const void*, void*, float, const float*, const float*, const float*, float*, void*) = nullptr;
     int (*status)() = nullptr;
 };
 inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
@@ -108,6 +109,7 @@ inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
         g.scaled = sym<decltype(g.scaled)>(g.lib, "fp8_gemm_scaled");
         g.accumulate = sym<decltype(g.accumulate)>(g.lib, "fp8_gemm_accumulate_f32");
         g.swiglu = sym<decltype(g.swiglu)>(g.lib, "fp8_gemm_swiglu");
+        g.fp8out = sym<decltype(g.fp8out)>(g.lib, "fp8_gemm_fp8out");
         g.status = sym<decltype(g.status)>(g.lib, "fp8_gemm_device_status");
     });
     if (!g.lib) throw Error(err);
@@ -145,6 +147,16 @@ inline void FP8GEMMSwiGLU(int M, int F, int K, uintptr_t A, uintptr_t Binterleav
                                              reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
                                              reinterpret_cast<float*>(amaxOut), detail::vp(stream));
     if (rc != 0) throw Error("fp8_gemm_swiglu: CUDA error " + std::to_string(rc));
+}
+// D (e4m3 [M,N]) = e4m3((*scaleD) * v), v = alpha * (*scaleA) * (*scaleB) * A x B^T; max|v| -> *amaxD (0: not wanted).
+// The delayed-scaling epilogue of fp8_matmul_fp8out (libs1/cublas_lt_wrapper_v3.c:220-229).
+inline void FP8GEMMFP8Out(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr_t D, float alpha, uintptr_t scaleA,
+                          uintptr_t scaleB, uintptr_t scaleD, uintptr_t amaxD, uintptr_t stream) {
+    const int rc = detail::gemm_lib().fp8out(M, N, K, detail::vp(A), detail::vp(B), detail::vp(D), alpha,
+                                             reinterpret_cast<const float*>(scaleA), reinterpret_cast<const float*>(scaleB),
+                                             reinterpret_cast<const float*>(scaleD), reinterpret_cast<float*>(amaxD),
+                                             detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm_fp8out: CUDA error " + std::to_string(rc));
 }
 // Host-side weight preparation for FP8GEMMSwiGLU: codes [2F, K] (gate rows first) -> [2*Fp, K], Fp = F rounded up to 128.
 inline std::vector<uint8_t> InterleaveGateUp(const std::vector<uint8_t>& gateUp, int F, int K) {

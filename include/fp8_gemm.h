@@ -74,6 +74,19 @@ FP8GEMM_API int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, cons
 FP8GEMM_API int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleaved, void* H, float alpha,
                                 const float* scale_a, const float* scale_b, float* amax_out, void* stream);
 
+/* Additive extension: e4m3 output with delayed scaling, the epilogue of the reference's cuBLASLt wrapper
+ * (fp8_matmul_fp8out, libs1/cublas_lt_wrapper_v3.c:157-229: D type CUDA_R_8F_E4M3 with D_SCALE_POINTER and
+ * AMAX_D_POINTER):
+ *   v = s * A . B^T,  s = alpha * (*scale_a) * (*scale_b), rounded to fp32;
+ *   D[M,N] (e4m3, row-major) = e4m3_rn_satfinite((*scale_d) * v);   *amax_d = max |v|  (before scale_d).
+ * scale_d is the MULTIPLIER applied before the conversion (the consumer dequantises with 1 / *scale_d); NULL = 1.
+ * amax_d may be NULL; otherwise the call clears it and the kernel reduces into it, so the caller can derive the
+ * next call's scale_d from it.  D must be 16-byte aligned and N a multiple of 16 for vector stores; other shapes
+ * take a byte-store path. */
+FP8GEMM_API int fp8_gemm_fp8out(int M, int N, int K, const void* A, const void* B, void* D, float alpha,
+                                const float* scale_a, const float* scale_b, const float* scale_d, float* amax_d,
+                                void* stream);
+
 /* Additive: device-side status of the current device.  The kernels bound every
  * wait; if a wait ever runs out they record a non-zero code here and exit
  * cleanly.  This call synchronises the device and returns (and clears) the

@@ -171,3 +171,67 @@ def test_swiglu_epilogue(cuda, built_libs, M, F, K):
     assert s2[1].item() == np.abs(hv).max()                       # the epilogue's amax is the max of what it wrote
     codes, scale, amax = O.quantize_f32(np.ascontiguousarray(hv))
     assert s2[0].item() == scale and np.array_equal(q.cpu().numpy(), codes)   # quantiser pass bit-exact on those values
+
+
+def _fp8out(a, b, alpha, sa, sb, sd, want_amax=True, guard=0):
+    """Run fp8_gemm_fp8out on host codes a [M,K], b [N,K]; returns (codes [M,N] (+guard bytes), amax)."""
+    from goml_b200 import fp8_gemm as G
+    M, K = a.shape
+    N = b.shape[0]
+    ad, bd = dev_u8(a), dev_u8(b)
+    d = torch.full((M * N + guard,), 0xAA, dtype=torch.uint8, device="cuda")
+    s = torch.tensor([sa, sb, sd, 123.0], dtype=torch.float32, device="cuda")
+    G.FP8GEMMFP8Out(M, N, K, ad.data_ptr(), bd.data_ptr(), d.data_ptr(), alpha, s.data_ptr(), s.data_ptr() + 4,
+                    s.data_ptr() + 8, s.data_ptr() + 12 if want_amax else 0)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    return d.cpu().numpy(), float(s[3].item())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 512), (130, 272, 144), (129, 250, 160), (16, 8192, 256), (300, 24, 1024)])
+def test_fp8out_exact_on_integer_data(cuda, built_libs, M, N, K):
+    # small-integer operands: every partial sum is exact in fp32, so the e4m3 codes and amax must be bit-exact
+    rng = np.random.default_rng(M * 7 + N)
+    av = rng.integers(-3, 4, size=(M, K)).astype(np.float32)
+    bv = rng.integers(-3, 4, size=(N, K)).astype(np.float32)
+    a, b = O.e4m3_encode(av), O.e4m3_encode(bv)
+    assert np.array_equal(O.e4m3_decode(a), av)
+    alpha, sa, sb, sd = np.float32(0.25), np.float32(0.5), np.float32(1.5), np.float32(0.37)
+    s = np.float32(np.float32(alpha * sa) * sb)
+    v = ((av.astype(np.float64) @ bv.astype(np.float64).T).astype(np.float32) * s).astype(np.float32)
+    ref = O.e4m3_encode((v * sd).astype(np.float32))
+    got, amax = _fp8out(a, b, float(alpha), float(sa), float(sb), float(sd), guard=64)
+    assert np.array_equal(got[:M * N].reshape(M, N), ref)
+    assert np.all(got[M * N:] == 0xAA)               # nothing written past the matrix
+    assert amax == float(np.abs(v).max())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (200, 136, 4096)])
+def test_fp8out_seeded_normal_within_one_code(cuda, built_libs, M, N, K):
+    # random data: the tensor-core sum differs from fp64 in the last bits, so a value near a rounding boundary may
+    # land on the neighbouring code; never further, and rarely
+    cfg = f"fp8out{M}x{N}x{K}"
+    a, sa, _ = O.quantize_f32(O.seeded_normal("A", (M, K), config=cfg))
+    b, sb, _ = O.quantize_f32(O.seeded_normal("B", (N, K), config=cfg))
+    v = O.gemm_f64(a, b, float(np.float32(sa) * np.float32(sb)))
+    amax_ref = np.abs(v).max()
+    sd = np.float32(448.0 / (1.1 * amax_ref))         # delayed scaling: a slightly stale amax
+    ref = O.e4m3_encode((v * float(sd)).astype(np.float32))
+    got, amax = _fp8out(a, b, 1.0, float(sa), float(sb), float(sd))
+    got = got.reshape(M, N)
+    assert abs(amax - amax_ref) <= 1e-5 * amax_ref * np.sqrt(K)
+    differ = got != ref
+    assert differ.mean() < 5e-3, differ.mean()
+    gi, ri = got[differ].astype(np.int32), ref[differ].astype(np.int32)
+    assert np.all((np.abs(gi - ri) == 1) | ((gi & 0x7F) + (ri & 0x7F) <= 1))   # neighbours, or +-0 / smallest subnormal
+
+
+def test_fp8out_saturates_and_amax_optional(cuda, built_libs):
+    M, N, K = 128, 64, 64
+    a = np.full((M, K), 0x40, np.uint8)              # 2.0
+    b = np.full((N, K), 0x40, np.uint8)
+    b[1::2] = 0xC0                                   # -2.0
+    got, amax = _fp8out(a, b, 1.0, 1.0, 1.0, 1e6, want_amax=False)
+    got = got.reshape(M, N)
+    assert np.all(got[:, 0::2] == 0x7E) and np.all(got[:, 1::2] == 0xFE)      # +-448, never NaN
+    assert amax == 123.0                              # not asked for: not written
