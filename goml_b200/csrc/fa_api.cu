@@ -189,13 +189,20 @@ fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* g) {
     if (!g) { set_err(ctx, "%s: null argument block", who); return FA_ERR_INVALID_ARG; }
     if (!ctx->arch_ok || !ctx->has_pool) { set_err(ctx, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
     if (!g->q || !g->k_cache || !g->v_cache || !g->o) { set_err(ctx, "%s: null pointer in q/k_cache/v_cache/o", who); return FA_ERR_INVALID_ARG; }
-    if (g->batch <= 0 || g->q_heads <= 0 || g->kv_heads <= 0 || g->s_max <= 0) { set_err(ctx, "%s: batch/heads/s_max must be > 0", who); return FA_ERR_INVALID_ARG; }
+    const bool paged = g->block_table != nullptr;
+    if (paged && (g->page_size <= 0 || g->page_size % 64 != 0 || g->max_pages_per_seq <= 0 || g->num_pages <= 0 ||
+                  (long long)g->page_size * g->max_pages_per_seq > 0x7fffffffLL)) {
+        set_err(ctx, "%s: paged cache needs page_size a positive multiple of 64, max_pages_per_seq > 0 and num_pages > 0", who);
+        return FA_ERR_INVALID_ARG;
+    }
+    const int s_max = paged ? g->page_size * g->max_pages_per_seq : g->s_max;
+    if (g->batch <= 0 || g->q_heads <= 0 || g->kv_heads <= 0 || s_max <= 0) { set_err(ctx, "%s: batch/heads/s_max must be > 0", who); return FA_ERR_INVALID_ARG; }
     if (g->head_dim != 64 && g->head_dim != 128) { set_err(ctx, "%s: head_dim must be 64 or 128", who); return FA_ERR_UNSUPPORTED_HD; }
     if (g->q_heads % g->kv_heads != 0 || g->q_heads / g->kv_heads > 16) {
         set_err(ctx, "%s: q_heads must be a multiple of kv_heads with at most 16 query heads per kv head", who);
         return FA_ERR_UNSUPPORTED_SHAPE;
     }
-    if (!g->seq_lens && (g->seq_len < 0 || g->seq_len > g->s_max)) { set_err(ctx, "%s: seq_len must be in [0, s_max]", who); return FA_ERR_INVALID_ARG; }
+    if (!g->seq_lens && (g->seq_len < 0 || g->seq_len > s_max)) { set_err(ctx, "%s: seq_len must be in [0, s_max]", who); return FA_ERR_INVALID_ARG; }
     if ((reinterpret_cast<uintptr_t>(g->q) & 3) || !aligned16(g->k_cache) || !aligned16(g->v_cache) || (reinterpret_cast<uintptr_t>(g->o) & 1)) {
         set_err(ctx, "%s: k_cache/v_cache must be 16-byte aligned, q 4-byte aligned", who);
         return FA_ERR_INVALID_ARG;
@@ -208,7 +215,8 @@ fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* g) {
     a.q = g->q; a.k_cache = g->k_cache; a.v_cache = g->v_cache; a.o = g->o; a.lse = static_cast<float*>(g->l_out);
     a.seq_lens = g->seq_lens;
     a.batch = g->batch; a.q_heads = g->q_heads; a.kv_heads = g->kv_heads; a.hd = g->head_dim;
-    a.s_max = g->s_max; a.seq_len = g->seq_len;
+    a.s_max = s_max; a.seq_len = g->seq_len;
+    a.block_table = g->block_table; a.page_size = g->page_size; a.max_pages = g->max_pages_per_seq; a.num_pages = g->num_pages;
     a.scale = g->scale; a.v_descale = (g->v_descale == 0.0f) ? 1.0f : g->v_descale;
     a.scale_q_dev = g->scale_q_dev; a.scale_k_dev = g->scale_k_dev; a.scale_v_dev = g->scale_v_dev;
     a.stream = reinterpret_cast<cudaStream_t>(g->stream);

@@ -79,6 +79,10 @@ struct DecodeParams {
     const float* sk;
     const float* sv;
     int splits, chunks_per_split;
+    // paged cache: k, v are [num_pages, Hkv, page_size, D]; logical chunk c of sequence b lives in page
+    // block_table[b * max_pages + c / chunks_per_page]
+    const int* block_table;
+    int page_size, max_pages, num_pages, chunks_per_page;
     float* ws_o;   // [B*Hkv, splits, ROWS, D] un-normalised partial outputs
     float* ws_ml;  // [B*Hkv, splits, ROWS, 2] (m in log2 units, l)
 };
@@ -96,7 +100,7 @@ struct Smem {
     static constexpr int BYTES = (OFF_V + V_BYTES) > MERGE_BYTES ? (OFF_V + V_BYTES) : MERGE_BYTES;
 };
 
-template <int D>
+template <int D, bool PAGED>
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) fa_decode_kernel(const DecodeParams p) {
     using S = Smem<D>;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -159,16 +163,44 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) fa_decode_kernel(const D
     // ldmatrix.x4: lanes 0-15 address the 16 key rows at d-tile n, lanes 16-31 the same rows at d-tile n + 1
     const uint32_t v_frag = sm + S::OFF_V + (16 * warp + (lane & 15)) * S::V_STRIDE + (lane >> 4) * 16;   // + n * 16
     const size_t lane_goff = (size_t)(key_l * PARTS + part_l) * 16;                      // byte offset of piece 0 inside a chunk
-    const uint8_t* kg = p.k + (size_t)bh * p.s_max * D + lane_goff;
-    const uint8_t* vg = p.v + (size_t)bh * p.s_max * D + lane_goff;
+    const uint8_t* kg = p.k + (PAGED ? 0 : (size_t)bh * p.s_max * D) + lane_goff;
+    const uint8_t* vg = p.v + (PAGED ? 0 : (size_t)bh * p.s_max * D) + lane_goff;
+    // paged: chunks are issued in order, so the position inside the block table advances incrementally (no division
+    // per chunk), and the entry of the next page is fetched when the last chunk of the current page is issued: its
+    // latency is hidden behind one loop iteration
+    const int* table = nullptr;      // entry of the page the next chunk to be issued lives in
+    int page_next = 0, within = 0;   // that entry's value; index of that chunk inside its page
+    size_t head_off = 0, page_stride = 0;
+    if (PAGED) {
+        const int pg = c_begin / p.chunks_per_page;
+        within = c_begin - pg * p.chunks_per_page;
+        table = p.block_table + (size_t)b * p.max_pages + pg;
+        if (c_begin < c_end) page_next = __ldg(table);
+        page_stride = (size_t)p.hkv * p.page_size * D;
+        head_off = (size_t)kvh * p.page_size * D;
+    }
     auto issue_chunk = [&](int c) {   // global -> ring stage (c - c_begin) % STAGES, one commit group per chunk
         const int st = (c - c_begin) % STAGES;
-        const size_t off = (size_t)c * CHUNK * D;
-        // keys past the end of this head's cache rows are not read (they would belong to the next head): zero-filled
-        const bool whole = (c + 1) * CHUNK <= p.s_max;
+        size_t off = (size_t)c * CHUNK * D;
+        // keys at or past seq_len are not read but zero-filled: past s_max they would belong to the next head, and
+        // below it they hold whatever the cache held before (possibly NaN codes; P = 0 there, but 0 x NaN would
+        // still poison O).  Only a sequence's last chunk has such keys.
+        const bool whole = (c + 1) * CHUNK <= seq_len;
+        bool none = false;
+        if (PAGED) {
+            const int page = page_next;
+            none = page < 0 || page >= p.num_pages;   // a table entry outside the pool: nothing is read, the keys count as zeros
+            // a chunk never crosses a page (page_size is a multiple of CHUNK)
+            off = none ? 0 : (size_t)page * page_stride + head_off + (size_t)within * (CHUNK * D);
+            if (++within == p.chunks_per_page) {
+                within = 0;
+                ++table;
+                if (c + 1 < c_end) page_next = __ldg(table);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < PER_THREAD; i++) {
-            const uint32_t nbytes = (whole || c * CHUNK + key_l + i * (32 / PARTS) < p.s_max) ? 16u : 0u;
+            const uint32_t nbytes = (!none && (whole || c * CHUNK + key_l + i * (32 / PARTS) < seq_len)) ? 16u : 0u;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(k_dst + st * S::K_BYTES + i * (32 / PARTS) * S::K_STRIDE),
                          "l"(kg + off + i * 512), "r"(nbytes)
                          : "memory");
@@ -426,18 +458,25 @@ cudaError_t launch_decode(const DecodeArgs& a) {
     p.ws_o = static_cast<float*>(a.workspace);
     p.ws_ml = p.ws_o ? p.ws_o + (size_t)a.batch * a.kv_heads * p.splits * ROWS * a.hd : nullptr;
     if (p.splits > 1 && !a.workspace) return cudaErrorInvalidValue;
+    p.block_table = a.block_table;
+    p.page_size = a.page_size; p.max_pages = a.max_pages; p.num_pages = a.num_pages;
+    p.chunks_per_page = a.block_table ? a.page_size / CHUNK : 1;
     const dim3 grid((unsigned)(a.batch * a.kv_heads), (unsigned)p.splits);
-    if (a.hd == 128) {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::BYTES);
+    auto run = [&](auto kernel, auto combine, int smem_bytes) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
-        fa_decode_kernel<128><<<grid, THREADS, Smem<128>::BYTES, a.stream>>>(p);
-        if (p.splits > 1) fa_decode_combine_kernel<128><<<grid.x, THREADS, 0, a.stream>>>(p);
-    } else {
-        cudaError_t e = cudaFuncSetAttribute(fa_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::BYTES);
-        if (e != cudaSuccess) return e;
-        fa_decode_kernel<64><<<grid, THREADS, Smem<64>::BYTES, a.stream>>>(p);
-        if (p.splits > 1) fa_decode_combine_kernel<64><<<grid.x, THREADS, 0, a.stream>>>(p);
-    }
+        kernel<<<grid, THREADS, smem_bytes, a.stream>>>(p);
+        if (p.splits > 1) combine<<<grid.x, THREADS, 0, a.stream>>>(p);
+        return cudaSuccess;
+    };
+    cudaError_t e;
+    if (a.hd == 128)
+        e = a.block_table ? run(fa_decode_kernel<128, true>, fa_decode_combine_kernel<128>, Smem<128>::BYTES)
+                          : run(fa_decode_kernel<128, false>, fa_decode_combine_kernel<128>, Smem<128>::BYTES);
+    else
+        e = a.block_table ? run(fa_decode_kernel<64, true>, fa_decode_combine_kernel<64>, Smem<64>::BYTES)
+                          : run(fa_decode_kernel<64, false>, fa_decode_combine_kernel<64>, Smem<64>::BYTES);
+    if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
 

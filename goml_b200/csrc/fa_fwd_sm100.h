@@ -44,6 +44,11 @@ struct DecodeArgs {
     const float* scale_v_dev = nullptr;
     void* workspace = nullptr;  // decode_workspace_bytes(...) bytes (0 when one split suffices)
     cudaStream_t stream;
+    // paged cache (block_table != nullptr): k_cache, v_cache are [num_pages, kv_heads, page_size, hd], page_size a
+    // multiple of 64; block_table [batch, max_pages] holds the page of each page_size-key range of a sequence and
+    // s_max = max_pages * page_size
+    const int* block_table = nullptr;
+    int page_size = 0, max_pages = 0, num_pages = 0;
 };
 // Longest key range any sequence can have in this call (s_max with per-sequence lengths, else seq_len).
 inline int decode_span(const DecodeArgs& a) { return a.seq_lens ? a.s_max : a.seq_len; }

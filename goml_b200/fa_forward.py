@@ -65,6 +65,7 @@ class DecodeArgs(C.Structure):
         ("scale", C.c_float), ("v_descale", C.c_float),
         ("scale_q_dev", C.c_void_p), ("scale_k_dev", C.c_void_p), ("scale_v_dev", C.c_void_p),
         ("stream", C.c_void_p),
+        ("block_table", C.c_void_p), ("page_size", C.c_int), ("max_pages_per_seq", C.c_int), ("num_pages", C.c_int),
     ]
 
 
@@ -192,13 +193,17 @@ class FAContext:
             raise FAError("fa_forward_ex", st, self._msg())
 
     def Decode(self, q, k_cache, v_cache, o, lOut, seq_lens, batch, q_heads, kv_heads, hd, s_max, seq_len, scale, v_descale=1.0,
-               scale_q_dev=0, scale_k_dev=0, scale_v_dev=0, stream=0) -> None:
+               scale_q_dev=0, scale_k_dev=0, scale_v_dev=0, stream=0, block_table=0, page_size=0, max_pages_per_seq=0,
+               num_pages=0) -> None:
         """One new token per sequence against an e4m3 KV cache [batch, kv_heads, s_max, hd], grouped-query heads;
-        seq_lens: device pointer to batch int32 lengths, or 0 to use seq_len for every sequence."""
+        seq_lens: device pointer to batch int32 lengths, or 0 to use seq_len for every sequence.  With block_table
+        (device pointer to int32 [batch, max_pages_per_seq]) the caches are page pools [num_pages, kv_heads, page_size,
+        hd] and s_max is ignored."""
         if not self.ptr:
             raise FAError("FAContext.Decode: nil ctx", FA_ERR_INVALID_ARG)
         a = DecodeArgs(q, k_cache, v_cache, o, lOut or None, seq_lens or None, batch, q_heads, kv_heads, hd, s_max, seq_len,
-                       scale, v_descale, scale_q_dev or None, scale_k_dev or None, scale_v_dev or None, stream or None)
+                       scale, v_descale, scale_q_dev or None, scale_k_dev or None, scale_v_dev or None, stream or None,
+                       block_table or None, page_size, max_pages_per_seq, num_pages)
         st = FALoad().fa_decode(self.ptr, C.byref(a))
         if st != FA_OK:
             raise FAError("fa_decode", st, self._msg())

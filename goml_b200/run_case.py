@@ -2,9 +2,10 @@
 
     python -m goml_b200.run_case fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
     python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
+    python -m goml_b200.run_case gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
     python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
-    python -m goml_b200.run_case decode B HQ HKV S D ITERS     # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing
+    python -m goml_b200.run_case decode B HQ HKV S D ITERS [PAGE]   # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing; PAGE: paged cache
     python -m goml_b200.run_case block B S D H F ITERS         # one fused FP8 decoder block (goml_b200.nn), random-init weights
 
 torch only allocates the device buffers; every launch goes through the C ABI.
@@ -39,6 +40,31 @@ def main(argv):
             G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, 0, 0, G.OutBF16, 0)
         torch.cuda.synchronize()
         assert G.device_status() == 0
+    elif kind == "gemm8":
+        # the e4m3-output epilogue beside the bf16 one on the same operands: ms and TFLOPS of each
+        M, N, K, iters = args
+        a = torch.randn(M, K, device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn(N, K, device="cuda").to(torch.float8_e4m3fn)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        d = torch.empty(M, N, dtype=torch.uint8, device="cuda")
+        s = torch.tensor([1.0, 1.0, 448.0 / (6.0 * K ** 0.5), 0.0], device="cuda")
+        runs = {
+            "bf16 out": lambda: G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, 0, 0, G.OutBF16, 0),
+            "e4m3 out + amax": lambda: G.FP8GEMMFP8Out(M, N, K, a.data_ptr(), b.data_ptr(), d.data_ptr(), 1.0, s.data_ptr(),
+                                                       s.data_ptr() + 4, s.data_ptr() + 8, s.data_ptr() + 12),
+        }
+        for name, fn in runs.items():
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            print(f"gemm {M}x{N}x{K} {name}: {ms:.4f} ms, {2.0 * M * N * K / ms / 1e9:.0f} TFLOPS")
+        assert G.device_status() == 0 and s[3].item() > 0
     elif kind == "quant":
         n, iters = args
         x = torch.randn(n, device="cuda")
@@ -67,13 +93,23 @@ def main(argv):
         print(f"block B={B} S={S} d={d} H={H} F={Fh}: {e0.elapsed_time(e1) / iters:.3f} ms per block")
         blk.close()
     elif kind == "decode":
-        B, hq, hkv, S, D, iters = args
+        # optional 7th argument: page size of a paged cache (pages of every sequence scattered over the pool)
+        B, hq, hkv, S, D, iters = args[:6]
+        page = args[6] if len(args) > 6 else 0
         ctx = F.FACreate()
         g = torch.Generator(device="cuda").manual_seed(0)
         q = torch.randn(B, hq, D, device="cuda", generator=g).mul_(0.5).to(torch.float8_e4m3fn)
         kc, vc = (torch.randn(B, hkv, S, D, device="cuda", generator=g).mul_(0.5).to(torch.float8_e4m3fn) for _ in range(2))
         o = torch.empty(B, hq, D, dtype=torch.float16, device="cuda")
-        fn = lambda: ctx.Decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, 0, B, hq, hkv, D, S, S, 1 / math.sqrt(D))
+        if page:
+            assert S % page == 0
+            per_seq = S // page
+            # the same bytes seen as a pool [B * per_seq, hkv, page, D]; a random table spreads each sequence over it
+            table = torch.randperm(B * per_seq, generator=g, device="cuda").to(torch.int32).view(B, per_seq).contiguous()
+            fn = lambda: ctx.Decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, 0, B, hq, hkv, D, 0, S, 1 / math.sqrt(D),
+                                    block_table=table.data_ptr(), page_size=page, max_pages_per_seq=per_seq, num_pages=B * per_seq)
+        else:
+            fn = lambda: ctx.Decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, 0, B, hq, hkv, D, S, S, 1 / math.sqrt(D))
         fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -85,7 +121,7 @@ def main(argv):
         ctx.DeviceStatus()
         us = e0.elapsed_time(e1) / iters * 1e3
         nbytes = 2 * B * hkv * S * D
-        print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
+        print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}{f' page={page}' if page else ''}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
     elif kind == "glue":
         B, S, d, H, Fh, iters = args
         T, hd, dev = B * S, d // H, "cuda"

@@ -172,7 +172,13 @@ FA_API fa_status_t fa_forward_noalloc(const fa_forward_args_t* args, char* err, 
  * [0, seq_lens[b]) (seq_lens: batch int32 values on the device, clamped to [0, s_max]) or, when seq_lens is NULL,
  * keys [0, seq_len).  scale = softmax_scale * scale_Q * scale_K, v_descale and the optional device scale pointers as
  * in fa_forward_ex.  A sequence with no visible key gets O = 0 and LSE = -inf.  HBM-bound: every cached key and value
- * is read once. */
+ * is read once.  Cache bytes at or past a sequence's length are never used, whatever they hold.
+ * Paged cache (block_table != NULL): k_cache, v_cache are pools [num_pages, kv_heads, page_size, head_dim], page_size
+ * a multiple of 64; block_table [batch, max_pages_per_seq] int32 on the device gives the pool page that holds keys
+ * [j * page_size, (j+1) * page_size) of sequence b at block_table[b * max_pages_per_seq + j]; s_max is then
+ * max_pages_per_seq * page_size (the field is ignored).  Only entries below ceil(seq_len / page_size) are read; an
+ * entry outside [0, num_pages) reads nothing and its keys count as zeros.  Zero the struct before filling it: with
+ * block_table == NULL the last four fields are ignored. */
 typedef struct fa_decode_args {
     const void* q;
     const void* k_cache;
@@ -188,6 +194,10 @@ typedef struct fa_decode_args {
     const float* scale_k_dev;
     const float* scale_v_dev;
     fa_stream_t stream;
+    const int* block_table;
+    int page_size;
+    int max_pages_per_seq;
+    int num_pages;
 } fa_decode_args_t;
 
 FA_API fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* args);
