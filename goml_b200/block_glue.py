@@ -22,6 +22,20 @@ class BlockGlueError(RuntimeError):
     pass
 
 
+class DecodeAppendArgs(C.Structure):
+    """fp8_decode_append_args_t (include/fp8_block.h)."""
+    _fields_ = [
+        ("qkv_bf16", C.c_void_p), ("cos_tab", C.c_void_p), ("sin_tab", C.c_void_p), ("positions", C.c_void_p),
+        ("q_out", C.c_void_p), ("q_scale_out", C.c_void_p), ("q_amax_out", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("seq_lens_out", C.c_void_p), ("block_table", C.c_void_p),
+        ("batch", C.c_int32), ("q_heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("s_max", C.c_int32), ("rope_rows", C.c_int32),
+        ("page_size", C.c_int32), ("max_pages_per_seq", C.c_int32), ("num_pages", C.c_int32), ("reserved", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 def _init():
     global _lib
     with _lock:
@@ -36,6 +50,7 @@ def _init():
                 "fp8_swiglu_quantize": [p, p, p, p, i, i, p],
                 "fp8_quantize_bf16": [p, p, p, p, z, p],
                 "fp8_residual_add": [p, p, z, p],
+                "fp8_decode_rope_append": [C.POINTER(DecodeAppendArgs)],
             }.items():
                 fn = getattr(lib, name)
                 fn.restype = C.c_int
@@ -81,3 +96,14 @@ def QuantizeBF16(x_bf16: int, q: int, scale: int, amax_in: int, n: int, stream: 
 
 def ResidualAdd(x: int, y_bf16: int, n: int, stream: int = 0) -> None:
     _check("fp8_residual_add", _init().fp8_residual_add(x, y_bf16, n, stream or None))
+
+
+def DecodeRopeAppend(qkv_bf16, cos_tab, sin_tab, positions, q_out, q_scale_out, q_amax_out, k_cache, v_cache, k_scale, v_scale,
+                     batch, q_heads, kv_heads, head_dim, s_max, rope_rows, seq_lens_out=0, block_table=0, page_size=0,
+                     max_pages_per_seq=0, num_pages=0, stream=0) -> None:
+    """Decode step: RoPE at positions[b] on the new token's Q and K, Q codes with a fresh per-tensor scale, K and V
+    codes (cache scales *k_scale, *v_scale) written at positions[b] of the contiguous or paged FP8 KV cache."""
+    a = DecodeAppendArgs(qkv_bf16, cos_tab, sin_tab, positions, q_out, q_scale_out, q_amax_out, k_cache, v_cache, k_scale, v_scale,
+                         seq_lens_out or None, block_table or None, batch, q_heads, kv_heads, head_dim, s_max, rope_rows,
+                         page_size, max_pages_per_seq, num_pages, 0, stream or None)
+    _check("fp8_decode_rope_append", _init().fp8_decode_rope_append(C.byref(a)))

@@ -442,6 +442,125 @@ __global__ void __launch_bounds__(THREADS) qkv_quant_kernel(const uint16_t* __re
     }
 }
 
+// ---------------------------------------------------------------------------------- decode step: RoPE + quantise + cache append
+// One item = 32 elements of one (sequence, head slot): slots [0, Hq) are query heads, [Hq, Hq+Hkv) key heads,
+// [Hq+Hkv, Hq+2Hkv) value heads of the new token's projection row.  Q and K items are 16 rotation pairs as above.
+struct DecAppend {
+    const uint16_t* qkv;
+    const float* cos_tab;
+    const float* sin_tab;
+    const int* positions;
+    uint8_t* q_out;
+    float* q_scale;
+    float* q_amax;
+    uint8_t* k_cache;
+    uint8_t* v_cache;
+    const float* k_scale;
+    const float* v_scale;
+    int* seq_lens_out;
+    const int* block_table;
+    int batch, hq, hkv, hd, s_max, table_rows, page_size, max_pages, num_pages;
+    uint32_t items;
+    FastDiv cph, slots;
+};
+// position of sequence b's new token, or -1 when it cannot be placed (an inactive slot, a full cache, no RoPE row)
+__device__ __forceinline__ int dec_position(const DecAppend& a, int b) {
+    const int pos = __ldg(a.positions + b);
+    const int cap = a.block_table ? a.page_size * a.max_pages : a.s_max;
+    return (pos >= 0 && pos < cap && pos < a.table_rows) ? pos : -1;
+}
+__device__ __forceinline__ void dec_values(const DecAppend& a, int b, int slot, int c, int pos, float* y) {
+    const int half = a.hd / 2;
+    const size_t row = ((size_t)b * (a.hq + 2 * a.hkv) + slot) * a.hd;
+    if (slot >= a.hq + a.hkv) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.qkv + row + 32 * c);
+#pragma unroll
+        for (int v = 0; v < 4; v++) bf16x8_to_f32(__ldg(src + v), y + 8 * v);
+        return;
+    }
+    float x0[16], x1[16];
+    const uint4* s0 = reinterpret_cast<const uint4*>(a.qkv + row + 16 * c);
+    const uint4* s1 = reinterpret_cast<const uint4*>(a.qkv + row + half + 16 * c);
+    bf16x8_to_f32(__ldg(s0), x0);
+    bf16x8_to_f32(__ldg(s0 + 1), x0 + 8);
+    bf16x8_to_f32(__ldg(s1), x1);
+    bf16x8_to_f32(__ldg(s1 + 1), x1 + 8);
+    const float* ct = a.cos_tab + (size_t)pos * half + 16 * c;
+    const float* st = a.sin_tab + (size_t)pos * half + 16 * c;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const float cc = __ldg(ct + i), ss = __ldg(st + i);
+        y[i] = __fsub_rn(__fmul_rn(x0[i], cc), __fmul_rn(x1[i], ss));
+        y[16 + i] = __fadd_rn(__fmul_rn(x0[i], ss), __fmul_rn(x1[i], cc));
+    }
+}
+__global__ void __launch_bounds__(THREADS) dec_q_amax_kernel(const DecAppend a) {
+    __shared__ float sh[THREADS / 32];
+    float m = 0.f;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < a.items; it += gridDim.x * blockDim.x) {
+        uint32_t q, c, b, slot;
+        a.cph.divmod(it, q, c);
+        a.slots.divmod(q, b, slot);
+        if ((int)slot >= a.hq) continue;
+        const int pos = dec_position(a, (int)b);
+        if (pos < 0) continue;
+        float y[32];
+        dec_values(a, (int)b, (int)slot, (int)c, pos, y);
+        m = absmax16(y + 16, absmax16(y, m));
+    }
+    m = block_max(m, sh);
+    if (threadIdx.x == 0) atomic_amax(a.q_amax, m);
+}
+__global__ void __launch_bounds__(THREADS) dec_append_kernel(const DecAppend a) {
+    const float q_sc = scale_from_amax(*a.q_amax);
+    const float inv_q = __fdiv_rn(1.0f, q_sc);
+    const float inv_k = __fdiv_rn(1.0f, __ldg(a.k_scale)), inv_v = __fdiv_rn(1.0f, __ldg(a.v_scale));
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.q_scale = q_sc;
+    const int half = a.hd / 2;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < a.items; it += gridDim.x * blockDim.x) {
+        uint32_t q, c, b, slot;
+        a.cph.divmod(it, q, c);
+        a.slots.divmod(q, b, slot);
+        const int pos = dec_position(a, (int)b);
+        if (slot == 0 && c == 0 && a.seq_lens_out) a.seq_lens_out[b] = pos < 0 ? 0 : pos + 1;
+        if ((int)slot < a.hq) {
+            uint8_t* dst = a.q_out + ((size_t)b * a.hq + slot) * a.hd;
+            if (pos < 0) {  // an inactive sequence: zero codes, nothing appended
+                *reinterpret_cast<uint4*>(dst + 16 * c) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dst + half + 16 * c) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            float y[32];
+            dec_values(a, (int)b, (int)slot, (int)c, pos, y);
+            *reinterpret_cast<uint4*>(dst + 16 * c) = quant16(y, inv_q);
+            *reinterpret_cast<uint4*>(dst + half + 16 * c) = quant16(y + 16, inv_q);
+            continue;
+        }
+        if (pos < 0) continue;
+        const bool is_v = (int)slot >= a.hq + a.hkv;
+        const int h = (int)slot - a.hq - (is_v ? a.hkv : 0);
+        size_t key_row;   // index of this (sequence, kv head, position) among the cache's rows of hd codes
+        if (a.block_table) {
+            const int pg = pos / a.page_size;
+            const int page = __ldg(a.block_table + (size_t)b * a.max_pages + pg);
+            if (page < 0 || page >= a.num_pages) continue;   // no page behind this position: nothing is written
+            key_row = ((size_t)page * a.hkv + h) * a.page_size + (pos - pg * a.page_size);
+        } else {
+            key_row = ((size_t)b * a.hkv + h) * a.s_max + pos;
+        }
+        float y[32];
+        dec_values(a, (int)b, (int)slot, (int)c, pos, y);
+        uint8_t* dst = (is_v ? a.v_cache : a.k_cache) + key_row * a.hd;
+        if (is_v) {
+            *reinterpret_cast<uint4*>(dst + 32 * c) = quant16(y, inv_v);
+            *reinterpret_cast<uint4*>(dst + 32 * c + 16) = quant16(y + 16, inv_v);
+        } else {
+            *reinterpret_cast<uint4*>(dst + 16 * c) = quant16(y, inv_k);
+            *reinterpret_cast<uint4*>(dst + half + 16 * c) = quant16(y + 16, inv_k);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- attention output: permute + quantise
 // item = 16 consecutive elements of one (token, head); out index order so that stores are contiguous
 struct ODivs {
@@ -657,6 +776,42 @@ int fp8_rope_quantize_qkv(const void* qkv_bf16, const float* cos_tab, const floa
         qkv_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, (uint32_t)items, seq_len, heads, head_dim, dv);
     qkv_quant_kernel<<<grid_for(items), THREADS, 0, s>>>(src, cos_tab, sin_tab, amaxes, scales, q_out, k_out, v_out, (uint32_t)items, seq_len,
                                                          heads, head_dim, dv);
+    return (int)cudaGetLastError();
+}
+
+int fp8_decode_rope_append(const fp8_decode_append_args_t* g) {
+    if (!g || !g->qkv_bf16 || !g->cos_tab || !g->sin_tab || !g->positions || !g->q_out || !g->q_scale_out || !g->q_amax_out ||
+        !g->k_cache || !g->v_cache || !g->k_scale || !g->v_scale)
+        return (int)cudaErrorInvalidValue;
+    if (g->batch < 0 || g->q_heads <= 0 || g->kv_heads <= 0 || (g->head_dim != 64 && g->head_dim != 128) || g->rope_rows <= 0)
+        return (int)cudaErrorInvalidValue;
+    if (g->block_table) {
+        if (g->page_size <= 0 || g->max_pages_per_seq <= 0 || g->num_pages <= 0 ||
+            (long long)g->page_size * g->max_pages_per_seq > 0x7fffffffLL)
+            return (int)cudaErrorInvalidValue;
+    } else if (g->s_max <= 0) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (misaligned(g->qkv_bf16) || misaligned(g->q_out) || misaligned(g->k_cache) || misaligned(g->v_cache)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)g->stream;
+    cudaError_t e = cudaMemsetAsync(g->q_amax_out, 0, sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    const int slots = g->q_heads + 2 * g->kv_heads;
+    const size_t items = (size_t)g->batch * slots * (g->head_dim / 32);
+    if (items >= (1ull << 31)) return (int)cudaErrorInvalidValue;
+    DecAppend a;
+    a.qkv = reinterpret_cast<const uint16_t*>(g->qkv_bf16);
+    a.cos_tab = g->cos_tab; a.sin_tab = g->sin_tab; a.positions = g->positions;
+    a.q_out = g->q_out; a.q_scale = g->q_scale_out; a.q_amax = g->q_amax_out;
+    a.k_cache = g->k_cache; a.v_cache = g->v_cache; a.k_scale = g->k_scale; a.v_scale = g->v_scale;
+    a.seq_lens_out = g->seq_lens_out; a.block_table = g->block_table;
+    a.batch = g->batch; a.hq = g->q_heads; a.hkv = g->kv_heads; a.hd = g->head_dim; a.s_max = g->s_max;
+    a.table_rows = g->rope_rows; a.page_size = g->page_size; a.max_pages = g->max_pages_per_seq; a.num_pages = g->num_pages;
+    a.items = (uint32_t)items;
+    a.cph = FastDiv(g->head_dim / 32);
+    a.slots = FastDiv(slots);
+    if (items > 0) dec_q_amax_kernel<<<grid_for(items), THREADS, 0, s>>>(a);
+    dec_append_kernel<<<grid_for(items), THREADS, 0, s>>>(a);
     return (int)cudaGetLastError();
 }
 

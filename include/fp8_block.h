@@ -86,6 +86,46 @@ FP8BLOCK_API int fp8_quantize_bf16(const void* x_bf16, uint8_t* q, float* scale_
 /* x[i] += y[i] (x fp32 residual stream, y bf16), n a multiple of 8. */
 FP8BLOCK_API int fp8_residual_add(float* x, const void* y_bf16, size_t n, void* stream);
 
+/* Decode step of quantised inference: the new token's projection row of every sequence -> RoPE at the token's
+ * position -> Q codes for fa_decode, and the K and V codes appended to the FP8 KV cache in place.  It is the device
+ * side of KVCache.Append(l, k, v) as sketched in runs/reports/F1_HF_INFERENCE_recon.md:186-196 (write position tCur
+ * of a [H_kv, S_max, hd] cache), fused with RoPE (battle_a_llm_f64ref.go:221-237) and the quantiser.
+ *   qkv_bf16   [batch, (q_heads + 2*kv_heads) * head_dim] bf16: query heads, then key heads, then value heads;
+ *   cos_tab, sin_tab [rope_rows, head_dim/2] fp32 (fp8_rope_table);
+ *   positions  [batch] int32 on the device: index of the new token = number of keys already cached.  A sequence whose
+ *              position is outside [0, min(capacity, rope_rows)) is inactive: its Q codes are zeros, nothing is
+ *              appended and its seq_lens_out entry is 0;
+ *   q_out      [batch, q_heads, head_dim] e4m3 with a fresh per-tensor scale (*q_scale_out = amax/448, *q_amax_out);
+ *   k_cache, v_cache: the layouts fa_decode reads -- [batch, kv_heads, s_max, head_dim], or with block_table != NULL
+ *              pools [num_pages, kv_heads, page_size, head_dim] (block_table [batch, max_pages_per_seq] int32; a
+ *              position whose table entry is outside [0, num_pages) is not written);
+ *   k_scale, v_scale: device pointers to the dequantisation scales the cache was written with; the new codes are
+ *              e4m3_rn_satfinite(clamp(x / scale)), i.e. values beyond 448 * scale saturate;
+ *   seq_lens_out [batch] int32 or NULL: positions[b] + 1, the lengths to pass to fa_decode next.
+ * head_dim 64 or 128.  Two passes over the Q part (amax, then codes); K and V are written in the second. */
+typedef struct fp8_decode_append_args {
+    const void* qkv_bf16;
+    const float* cos_tab;
+    const float* sin_tab;
+    const int32_t* positions;
+    uint8_t* q_out;
+    float* q_scale_out;
+    float* q_amax_out;
+    uint8_t* k_cache;
+    uint8_t* v_cache;
+    const float* k_scale;
+    const float* v_scale;
+    int32_t* seq_lens_out;
+    const int32_t* block_table;
+    int32_t batch, q_heads, kv_heads, head_dim;
+    int32_t s_max, rope_rows;
+    int32_t page_size, max_pages_per_seq, num_pages;
+    int32_t reserved;
+    void* stream;
+} fp8_decode_append_args_t;
+
+FP8BLOCK_API int fp8_decode_rope_append(const fp8_decode_append_args_t* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -90,3 +90,49 @@ def decode_attention_f64(q, k_cache, v_cache, seq_lens, scale, v_descale=1.0):
             out[b, h] = (p @ vf[b, kv, :n]) / p.sum() * v_descale
             lse[b, h] = m + np.log(p.sum())
     return out, lse
+
+
+def quantize_fixed_scale(x, scale):
+    """Codes of x for a tensor whose dequantisation scale is already fixed (an FP8 KV cache): the quantiser's second
+    pass (libs1/fp8_quantize_v2.cu:100-121) with inv = 1/scale in fp32, clamp to +-448, round to nearest even."""
+    inv = f32(1.0) / f32(scale)
+    return O.e4m3_encode(np.clip(np.asarray(x, f32) * inv, f32(-448.0), f32(448.0)).astype(f32))
+
+
+def decode_rope_append(qkv, cos, sin, positions, k_cache, v_cache, k_scale, v_scale, Hq, Hkv, hd):
+    """The new token of every sequence: qkv [B, (Hq + 2*Hkv) * hd] float32 values of bf16 (query heads, key heads,
+    value heads), half-split RoPE at positions[b] on Q and K (battle_a_llm_f64ref.go:221-237, evaluated in fp32: each
+    product rounded, one add), Q quantised per tensor, K and V quantised with the cache's scales and written at
+    position positions[b] of k_cache / v_cache [B, Hkv, Smax, hd] (KVCache.Append of
+    runs/reports/F1_HF_INFERENCE_recon.md:186-196).  Sequences whose position is outside [0, min(Smax, rows of the
+    RoPE table)) are inactive: zero Q codes, no append, length 0.
+    Returns (q_codes [B, Hq, hd], q_scale, q_amax, k_cache', v_cache', seq_lens)."""
+    qkv = np.asarray(qkv, f32)
+    B = qkv.shape[0]
+    Smax = k_cache.shape[2]
+    half = hd // 2
+    rows = qkv.reshape(B, Hq + 2 * Hkv, hd)
+    kc, vc = k_cache.copy(), v_cache.copy()
+    qv = np.zeros((B, Hq, hd), f32)
+    active = np.zeros(B, bool)
+    seq_lens = np.zeros(B, np.int32)
+
+    def rope(a, pos):
+        x0, x1 = a[..., :half], a[..., half:]
+        c, s = cos[pos], sin[pos]
+        return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1).astype(f32)
+
+    for b in range(B):
+        pos = int(positions[b])
+        if not (0 <= pos < min(Smax, cos.shape[0])):
+            continue
+        active[b] = True
+        seq_lens[b] = pos + 1
+        qv[b] = rope(rows[b, :Hq], pos)
+        kc[b, :, pos] = quantize_fixed_scale(rope(rows[b, Hq:Hq + Hkv], pos), k_scale)
+        vc[b, :, pos] = quantize_fixed_scale(rows[b, Hq + Hkv:], v_scale)
+    amax = f32(np.abs(qv[active]).max()) if active.any() else f32(0.0)
+    scale = f32(amax / f32(448.0)) if amax > 1e-12 else f32(1.0)
+    q_codes = quantize_fixed_scale(qv, scale)
+    q_codes[~active] = 0
+    return q_codes, scale, amax, kc, vc, seq_lens
