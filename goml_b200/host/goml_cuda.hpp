@@ -33,6 +33,7 @@
 #include <vector>
 
 #include "../../include/fa_sm120.h"
+#include "../../include/fp8_block.h"   // fp8_decode_append_args_t (the functions are bound at run time, not linked)
 
 namespace goml {
 namespace cuda {
@@ -343,6 +344,7 @@ struct BlockLib {
     int (*swiglu_q)(const void*, uint8_t*, float*, float*, int, int, void*) = nullptr;
     int (*quant_bf16)(const void*, uint8_t*, float*, const float*, size_t, void*) = nullptr;
     int (*residual_add)(float*, const void*, size_t, void*) = nullptr;
+    int (*decode_append)(const fp8_decode_append_args_t*) = nullptr;
 };
 inline BlockLib& block_lib() {
     static BlockLib b;
@@ -358,6 +360,7 @@ inline BlockLib& block_lib() {
         b.swiglu_q = sym<decltype(b.swiglu_q)>(b.lib, "fp8_swiglu_quantize");
         b.quant_bf16 = sym<decltype(b.quant_bf16)>(b.lib, "fp8_quantize_bf16");
         b.residual_add = sym<decltype(b.residual_add)>(b.lib, "fp8_residual_add");
+        b.decode_append = sym<decltype(b.decode_append)>(b.lib, "fp8_decode_rope_append");
     });
     if (!b.lib) throw Error(err);
     return b;
@@ -401,6 +404,11 @@ inline void QuantizeBF16(uintptr_t xBF16, uintptr_t q, uintptr_t scale, uintptr_
 }
 inline void ResidualAdd(uintptr_t x, uintptr_t yBF16, size_t n, uintptr_t stream = 0) {
     detail::block_check("fp8_residual_add", detail::block_lib().residual_add(detail::tp<float>(x), detail::vp(yBF16), n, detail::vp(stream)));
+}
+// Decode step: RoPE + quantise of the new token of every sequence, K and V appended to the FP8 KV cache in place
+// (KVCache.Append of runs/reports/F1_HF_INFERENCE_recon.md:186-196).  Zero-initialise the struct, fill, pass.
+inline void DecodeRopeAppend(const fp8_decode_append_args_t& a) {
+    detail::block_check("fp8_decode_rope_append", detail::block_lib().decode_append(&a));
 }
 
 // --------------------------------------------------------------------------- multi-GPU manager

@@ -2,6 +2,7 @@
 
     python -m goml_b200.run_case fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
     python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
+    python -m goml_b200.run_case decstep B HQ HKV S D ITERS    # new token's RoPE + quantise + cache append, then fa_decode
     python -m goml_b200.run_case gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
     python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
@@ -122,6 +123,39 @@ def main(argv):
         us = e0.elapsed_time(e1) / iters * 1e3
         nbytes = 2 * B * hkv * S * D
         print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}{f' page={page}' if page else ''}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
+    elif kind == "decstep":
+        # one decode step's attention part: RoPE + quantise + cache append of the new token, then fa_decode
+        from . import block_glue as BG
+        B, hq, hkv, S, D, iters = args
+        ctx = F.FACreate()
+        g = torch.Generator(device="cuda").manual_seed(0)
+        kc, vc = (torch.randn(B, hkv, S, D, device="cuda", generator=g).mul_(0.5).to(torch.float8_e4m3fn) for _ in range(2))
+        qkv = torch.randn(B, (hq + 2 * hkv) * D, device="cuda", generator=g).bfloat16()
+        cos, sin = torch.empty(S, D // 2, device="cuda"), torch.empty(S, D // 2, device="cuda")
+        BG.RopeTable(cos.data_ptr(), sin.data_ptr(), S, D, 10000.0)
+        pos = torch.full((B,), S - 1, dtype=torch.int32, device="cuda")
+        lens = torch.zeros(B, dtype=torch.int32, device="cuda")
+        q = torch.empty(B, hq, D, dtype=torch.uint8, device="cuda")
+        o = torch.empty(B, hq, D, dtype=torch.float16, device="cuda")
+        sc = torch.tensor([0.0, 0.0, 1.0, 1.0], device="cuda")
+        def append():
+            BG.DecodeRopeAppend(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(), q.data_ptr(), sc.data_ptr(), sc.data_ptr() + 4,
+                                kc.data_ptr(), vc.data_ptr(), sc.data_ptr() + 8, sc.data_ptr() + 12, B, hq, hkv, D, S, S, seq_lens_out=lens.data_ptr())
+        def attend():
+            ctx.Decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, lens.data_ptr(), B, hq, hkv, D, S, 0, 1 / math.sqrt(D), 1.0,
+                       scale_q_dev=sc.data_ptr())
+        for name, fn in (("append", append), ("append + attend", lambda: (append(), attend()))):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            print(f"decstep B={B} Hq={hq} Hkv={hkv} S={S} D={D} {name}: {e0.elapsed_time(e1) / iters * 1e3:8.1f} us")
+        ctx.DeviceStatus()
+        assert bool(torch.isfinite(o.float()).all()) and int(lens[0]) == S
     elif kind == "glue":
         B, S, d, H, Fh, iters = args
         T, hd, dev = B * S, d // H, "cuda"

@@ -66,6 +66,7 @@ static int run_cpu(const char* libs_dir) {
     CHECK(thrown([] { ResidualAdd(64, 64, 12, 0); }) == "fp8_residual_add: CUDA error 1");
     CHECK(thrown([] { FP8GEMMSwiGLU(8, 0, 32, 16, 16, 16, 1.0f, 0, 0, 16, 0); }) == "fp8_gemm_swiglu: CUDA error 1");
     CHECK(thrown([] { FP8GEMMFP8Out(8, 8, 32, 16, 16, 0, 1.0f, 0, 0, 0, 0, 0); }) == "fp8_gemm_fp8out: CUDA error 1");
+    CHECK(thrown([] { fp8_decode_append_args_t a{}; a.batch = 1; DecodeRopeAppend(a); }) == "fp8_decode_rope_append: CUDA error 1");
     {   // weight layout for the SwiGLU GEMM: F = 130 -> two column blocks, the second one mostly padding
         const int F = 130, K = 4;
         std::vector<uint8_t> w((size_t)2 * F * K);
