@@ -61,3 +61,36 @@ def test_glue_restatements_agree_with_the_block_restatement():
     # RoPE tables: fp64 angles rounded once
     c, s = glue.rope_table(S, d // H, 10000.0)
     assert c.dtype == np.float32 and np.abs(c.astype(np.float64) ** 2 + s.astype(np.float64) ** 2 - 1).max() <= 3e-7
+
+
+def test_decode_append_restatement_properties():
+    # the appended K row decodes to RoPE(k) within one e4m3 step of the cache scale, positions outside the cache are
+    # inactive, nothing but the appended rows changes, and position 0 (angle 0) leaves Q and K un-rotated
+    B, Hq, Hkv, S, hd = 4, 4, 2, 32, 64
+    cos, sin = glue.rope_table(S, hd, 10000.0)
+    qkv = O.round_bf16(O.seeded_normal("qkv", (B, (Hq + 2 * Hkv) * hd), config="append-cpu")).astype(np.float32)
+    k, sk, _ = O.quantize_f32(O.seeded_normal("k", (B, Hkv, S, hd), config="append-cpu"))
+    v, sv, _ = O.quantize_f32(O.seeded_normal("v", (B, Hkv, S, hd), config="append-cpu"))
+    positions = [0, 7, S, -1]
+    qc, qs, qa, kc, vc, lens = glue.decode_rope_append(qkv, cos, sin, positions, k, v, sk, sv, Hq, Hkv, hd)
+    assert list(lens) == [1, 8, 0, 0]
+    assert np.all(qc[2:] == 0) and np.array_equal(kc[2:], k[2:]) and np.array_equal(vc[2:], v[2:])
+    changed = np.zeros_like(k, bool)
+    changed[0, :, 0] = changed[1, :, 7] = True
+    assert np.array_equal(kc[~changed], k[~changed]) and np.array_equal(vc[~changed], v[~changed])
+    rows = qkv.reshape(B, Hq + 2 * Hkv, hd)
+    # position 0: cos = 1, sin = 0 -> codes of the un-rotated rows
+    assert np.array_equal(kc[0, :, 0], glue.quantize_fixed_scale(rows[0, Hq:Hq + Hkv], sk))
+    assert np.array_equal(vc[1, :, 7], glue.quantize_fixed_scale(rows[1, Hq + Hkv:], sv))
+    assert qs == np.float32(qa / np.float32(448.0))
+    # rotation preserves the norm of every (i, i + hd/2) pair
+    kd = O.e4m3_decode(kc[1, :, 7]).astype(np.float64) * float(sk)
+    kin = rows[1, Hq:Hq + Hkv].astype(np.float64)
+    n_out = kd[:, :hd // 2] ** 2 + kd[:, hd // 2:] ** 2
+    n_in = kin[:, :hd // 2] ** 2 + kin[:, hd // 2:] ** 2
+    assert np.abs(np.sqrt(n_out) - np.sqrt(n_in)).max() <= 0.07 * np.abs(kin).max()    # one e4m3 step (2^-4 relative)
+
+
+def test_fixed_scale_quantiser_saturates():
+    codes = glue.quantize_fixed_scale(np.array([1e6, -1e6, 0.0, 448.0, 0.5], np.float32), 1.0)
+    assert list(codes) == [0x7E, 0xFE, 0x00, 0x7E, 0x30]
