@@ -522,7 +522,12 @@ __global__ void __launch_bounds__(THREADS) dec_append_kernel(const DecAppend a) 
         a.cph.divmod(it, q, c);
         a.slots.divmod(q, b, slot);
         const int pos = dec_position(a, (int)b);
-        if (slot == 0 && c == 0 && a.seq_lens_out) a.seq_lens_out[b] = pos < 0 ? 0 : pos + 1;
+        if (slot == 0 && c == 0 && a.seq_lens_out) {
+            // an inactive slot keeps its length: 0 for a negative position, the capacity for a full cache
+            const int raw = __ldg(a.positions + b);
+            const int cap = a.block_table ? a.page_size * a.max_pages : a.s_max;
+            a.seq_lens_out[b] = pos >= 0 ? pos + 1 : (raw < 0 ? 0 : min(raw, cap));
+        }
         if ((int)slot < a.hq) {
             uint8_t* dst = a.q_out + ((size_t)b * a.hq + slot) * a.hd;
             if (pos < 0) {  // an inactive sequence: zero codes, nothing appended

@@ -86,6 +86,28 @@ def rope_half_split(x: torch.Tensor, theta: float) -> torch.Tensor:
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
 
 
+class FP8KVCache:
+    """One layer's FP8 KV cache: K and V codes [batch, heads, s_max, hd] with one dequantisation scale each, fixed
+    when the prompt is written, and the per-sequence lengths on the device.  The structure of the KVCache sketched in
+    goml's runs/reports/F1_HF_INFERENCE_recon.md:186-196 (Append at position tCur, K()/V() views), holding e4m3 codes
+    instead of fp32 and S_max allocated up front."""
+
+    def __init__(self, batch: int, heads: int, s_max: int, hd: int, device="cuda"):
+        self.B, self.H, self.s_max, self.hd = batch, heads, s_max, hd
+        self.k = torch.zeros((batch, heads, s_max, hd), dtype=torch.uint8, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.scales = torch.ones(2, dtype=torch.float32, device=device)      # k_scale, v_scale
+        self.lens = torch.zeros(batch, dtype=torch.int32, device=device)     # keys cached per sequence
+        self._lens_next = torch.zeros_like(self.lens)
+
+    def fill(self, k_codes, v_codes, scales, S: int) -> None:
+        """Prompt phase: K/V codes [batch*heads, S, hd] as the prefill quantiser wrote them, and their two scales."""
+        self.k[:, :, :S].copy_(k_codes.view(self.B, self.H, S, self.hd))
+        self.v[:, :, :S].copy_(v_codes.view(self.B, self.H, S, self.hd))
+        self.scales.copy_(scales)
+        self.lens.fill_(S)
+
+
 class FP8DecoderBlock:
     """Llama-style block: RMSNorm -> QKV -> RoPE -> causal FP8 attention -> O -> residual -> RMSNorm -> SwiGLU -> residual."""
 
@@ -122,9 +144,10 @@ class FP8DecoderBlock:
             self._rope[S] = (cos, sin)
         return self._rope[S]
 
-    def forward_fused(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+    def forward_fused(self, x: torch.Tensor, B: int, S: int, cache: "FP8KVCache | None" = None) -> torch.Tensor:
         """The block with every glue op fused with the quantiser of its consumer and both residual adds done in
-        the GEMM epilogues, SwiGLU in the gate/up GEMM's epilogue: 9 library calls, no torch math."""
+        the GEMM epilogues, SwiGLU in the gate/up GEMM's epilogue: 9 library calls, no torch math.
+        With `cache`, the K and V codes of the prompt and their scales are also stored there for decode_step."""
         dev, T, d, H, hd, Fh = x.device, B * S, self.d, self.H, self.hd, self.F
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
@@ -140,13 +163,53 @@ class FP8DecoderBlock:
         qc, kc, vc, s3 = u8(B * H, S, hd), u8(B * H, S, hd), u8(B * H, S, hd), sa(6)   # scales[3], amaxes[3]
         BG.RopeQuantizeQKV(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                            s3.data_ptr(), s3.data_ptr() + 12, B, S, H, hd, sh)
+        if cache is not None:
+            cache.fill(kc, vc, s3[1:3], S)
         o = torch.empty((B * H, S, hd), dtype=torch.float16, device=dev)
         self.fa.ForwardEx(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), 0, B * H, S, hd, 1, 0, 1.0 / math.sqrt(hd), 1.0,
                           s3.data_ptr(), s3.data_ptr() + 4, s3.data_ptr() + 8, sh)
         oq = FP8Tensor(u8(T, d), sa())
         BG.PermuteQuantizeHeads(o.data_ptr(), oq.codes.data_ptr(), oq.sa.data_ptr(), oq.sa.data_ptr() + 4, B, S, H, hd, sh)
         self.o.accumulate_into(oq, T, h)                         # h += attention projection, in the GEMM epilogue
-        # feed-forward half
+        return self._feed_forward(h, T)
+
+    def decode_step(self, x: torch.Tensor, cache: FP8KVCache) -> torch.Tensor:
+        """One new token per sequence: x [batch, d] fp32 -> [batch, d] fp32, the token's K and V appended to `cache` at
+        position cache.lens[b] (quantised with the cache's scales) and cache.lens advanced.  Ten library calls:
+        RMSNorm+quantise -> QKV GEMM -> RoPE+quantise+append -> decode attention -> quantise -> O GEMM (residual in the
+        epilogue) -> the feed-forward half of forward_fused."""
+        dev, B, d, H, hd = x.device, x.shape[0], self.d, self.H, self.hd
+        assert (B, H, hd) == (cache.B, cache.H, cache.hd)
+        sh = torch.cuda.current_stream().cuda_stream
+        u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
+        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        h = x.float().clone()
+        rstd = torch.empty(B, dtype=torch.float32, device=dev)
+        cos, sin = self.rope_tables(cache.s_max, dev)
+        xq = FP8Tensor(u8(B, d), sa())
+        BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm1.data_ptr(), xq.codes.data_ptr(), xq.sa.data_ptr(), xq.sa.data_ptr() + 4,
+                           rstd.data_ptr(), B, d, self.eps, sh)
+        qkv = self.qkv.forward_codes(xq, B)                      # [B, (H + 2H) * hd] bf16: Q heads, K heads, V heads
+        qc, qs = u8(B, H, hd), sa()
+        BG.DecodeRopeAppend(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), cache.lens.data_ptr(), qc.data_ptr(), qs.data_ptr(),
+                            qs.data_ptr() + 4, cache.k.data_ptr(), cache.v.data_ptr(), cache.scales.data_ptr(), cache.scales.data_ptr() + 4,
+                            B, H, H, hd, cache.s_max, cache.s_max, seq_lens_out=cache._lens_next.data_ptr(), stream=sh)
+        cache.lens, cache._lens_next = cache._lens_next, cache.lens
+        o = torch.empty((B, H, hd), dtype=torch.float16, device=dev)
+        self.fa.Decode(qc.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), o.data_ptr(), 0, cache.lens.data_ptr(), B, H, H, hd,
+                       cache.s_max, 0, 1.0 / math.sqrt(hd), 1.0, qs.data_ptr(), cache.scales.data_ptr(), cache.scales.data_ptr() + 4, sh)
+        oq = FP8Tensor(u8(B, d), sa())
+        BG.PermuteQuantizeHeads(o.data_ptr(), oq.codes.data_ptr(), oq.sa.data_ptr(), oq.sa.data_ptr() + 4, B, 1, H, hd, sh)
+        self.o.accumulate_into(oq, B, h)
+        return self._feed_forward(h, B)
+
+    def _feed_forward(self, h: torch.Tensor, T: int) -> torch.Tensor:
+        """h [T, d] fp32 += W_down(silu(W_gate n) * W_up n), n = RMSNorm(h): in place, three GEMM-library calls."""
+        dev, d, Fh = h.device, self.d, self.F
+        sh = torch.cuda.current_stream().cuda_stream
+        u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
+        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        rstd = torch.empty(T, dtype=torch.float32, device=dev)
         xq2 = FP8Tensor(u8(T, d), sa())
         BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),
                            xq2.sa.data_ptr() + 4, rstd.data_ptr(), T, d, self.eps, sh)
@@ -159,10 +222,11 @@ class FP8DecoderBlock:
         self.down.accumulate_into(hq, T, h)                      # h += feed-forward output
         return h
 
-    def __call__(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, B: int, S: int, cache: "FP8KVCache | None" = None) -> torch.Tensor:
         """x [B*S, d] fp32 -> [B*S, d] fp32."""
+        assert cache is None or self.fused, "the KV cache is written by the fused path"
         if self.fused:
-            return self.forward_fused(x, B, S)
+            return self.forward_fused(x, B, S, cache)
         x = x.float()
         x = x + self.o(self.attention(rms_norm(x, self.norm1, self.eps), B, S)).float()
         gu = self.gate_up(rms_norm(x, self.norm2, self.eps)).float()

@@ -94,14 +94,16 @@ FP8BLOCK_API int fp8_residual_add(float* x, const void* y_bf16, size_t n, void* 
  *   cos_tab, sin_tab [rope_rows, head_dim/2] fp32 (fp8_rope_table);
  *   positions  [batch] int32 on the device: index of the new token = number of keys already cached.  A sequence whose
  *              position is outside [0, min(capacity, rope_rows)) is inactive: its Q codes are zeros, nothing is
- *              appended and its seq_lens_out entry is 0;
+ *              appended and its length is left as it is (seq_lens_out = 0 for a negative position, else
+ *              min(position, capacity): a full cache stays full instead of wrapping around);
  *   q_out      [batch, q_heads, head_dim] e4m3 with a fresh per-tensor scale (*q_scale_out = amax/448, *q_amax_out);
  *   k_cache, v_cache: the layouts fa_decode reads -- [batch, kv_heads, s_max, head_dim], or with block_table != NULL
  *              pools [num_pages, kv_heads, page_size, head_dim] (block_table [batch, max_pages_per_seq] int32; a
  *              position whose table entry is outside [0, num_pages) is not written);
  *   k_scale, v_scale: device pointers to the dequantisation scales the cache was written with; the new codes are
  *              e4m3_rn_satfinite(clamp(x / scale)), i.e. values beyond 448 * scale saturate;
- *   seq_lens_out [batch] int32 or NULL: positions[b] + 1, the lengths to pass to fa_decode next.
+ *   seq_lens_out [batch] int32 or NULL: positions[b] + 1 for active sequences, the lengths to pass to fa_decode
+ *              next (and the next step's positions); must not alias positions.
  * head_dim 64 or 128.  Two passes over the Q part (amax, then codes); K and V are written in the second. */
 typedef struct fp8_decode_append_args {
     const void* qkv_bf16;

@@ -70,3 +70,49 @@ def decoder_block(x, B, S, H, wqkv, wo, wgate_up, wdown, norm1, norm2, eps=1e-5,
         keep["h"] = O.round_bf16(keep["h"]).astype(np.float64)
     keep["ffn"] = _linear(keep["h"], wdown, round_out=not residual_in_epilogue)
     return x + keep["ffn"]
+
+
+def decoder_block_decode_step(x, positions, k_cache, v_cache, k_scale, v_scale, H, wqkv, wo, wgate_up, wdown, norm1, norm2,
+                              eps=1e-5, theta=10000.0, intermediates=None):
+    """One new token per sequence through the same block (fp64, the product's quantisation points): x [B, d] is the
+    token's residual stream, k_cache / v_cache [B, H, Smax, hd] e4m3 codes with dequantisation scales k_scale / v_scale,
+    positions[b] the number of keys already cached.  The token's K (after RoPE at its position) and V are quantised
+    with the cache's scales and written at positions[b] (KVCache.Append of runs/reports/F1_HF_INFERENCE_recon.md:186-196),
+    then the token attends to keys [0, positions[b]] (the single-row case of the causal attention of
+    internal/abjexam/llama_hf_f64ref.go:94-178).  The residual adds and SwiGLU use un-rounded projections, as the fused
+    product path does.  Returns (y [B, d], k_cache', v_cache')."""
+    from oracle import glue
+    x = x.astype(np.float64)
+    B, d = x.shape
+    hd = d // H
+    Fh = wdown.shape[1]
+    half = hd // 2
+    keep = intermediates if intermediates is not None else {}
+    keep["xn1"] = _rms_norm(x, norm1, eps)
+    keep["qkv"] = _linear(keep["xn1"], wqkv)
+    rows = keep["qkv"].reshape(B, 3, H, hd)
+    freq = theta ** (-2.0 * np.arange(half) / hd)
+    ang = np.asarray(positions, np.float64)[:, None, None] * freq[None, None, :]
+    c, s = np.cos(ang), np.sin(ang)
+
+    def rope(a):
+        x0, x1 = a[..., :half], a[..., half:]
+        return np.concatenate([x0 * c - x1 * s, x0 * s + x1 * c], axis=-1)
+
+    q, k, v = rope(rows[:, 0]), rope(rows[:, 1]), rows[:, 2]
+    qq, sq, _ = O.quantize_f32(np.ascontiguousarray(q, np.float32))
+    kc, vc = k_cache.copy(), v_cache.copy()
+    for b in range(B):
+        kc[b, :, int(positions[b])] = glue.quantize_fixed_scale(k[b].astype(np.float32), k_scale)
+        vc[b, :, int(positions[b])] = glue.quantize_fixed_scale(v[b].astype(np.float32), v_scale)
+    scale = float(np.float32(1.0 / math.sqrt(hd)) * np.float32(sq) * np.float32(k_scale))
+    o, _ = glue.decode_attention_f64(qq, kc, vc, np.asarray(positions) + 1, scale, float(v_scale))
+    keep["attn"] = O.round_fp16(o).astype(np.float64).reshape(B, d)
+    keep["ao"] = _linear(keep["attn"], wo, round_out=False)
+    x = x + keep["ao"]
+    keep["xn2"] = _rms_norm(x, norm2, eps)
+    keep["gu"] = _linear(keep["xn2"], wgate_up, round_out=False)
+    g, u = keep["gu"][:, :Fh], keep["gu"][:, Fh:]
+    keep["h"] = O.round_bf16(g / (1.0 + np.exp(-g)) * u).astype(np.float64)
+    keep["ffn"] = _linear(keep["h"], wdown, round_out=False)
+    return x + keep["ffn"], kc, vc

@@ -105,7 +105,7 @@ def decode_rope_append(qkv, cos, sin, positions, k_cache, v_cache, k_scale, v_sc
     product rounded, one add), Q quantised per tensor, K and V quantised with the cache's scales and written at
     position positions[b] of k_cache / v_cache [B, Hkv, Smax, hd] (KVCache.Append of
     runs/reports/F1_HF_INFERENCE_recon.md:186-196).  Sequences whose position is outside [0, min(Smax, rows of the
-    RoPE table)) are inactive: zero Q codes, no append, length 0.
+    RoPE table)) are inactive: zero Q codes, no append, length unchanged (0 for a negative position, else min(position, Smax)).
     Returns (q_codes [B, Hq, hd], q_scale, q_amax, k_cache', v_cache', seq_lens)."""
     qkv = np.asarray(qkv, f32)
     B = qkv.shape[0]
@@ -125,6 +125,7 @@ def decode_rope_append(qkv, cos, sin, positions, k_cache, v_cache, k_scale, v_sc
     for b in range(B):
         pos = int(positions[b])
         if not (0 <= pos < min(Smax, cos.shape[0])):
+            seq_lens[b] = 0 if pos < 0 else min(pos, Smax)      # inactive: the length stays as it is
             continue
         active[b] = True
         seq_lens[b] = pos + 1

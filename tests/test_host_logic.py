@@ -73,7 +73,7 @@ def test_decode_append_restatement_properties():
     v, sv, _ = O.quantize_f32(O.seeded_normal("v", (B, Hkv, S, hd), config="append-cpu"))
     positions = [0, 7, S, -1]
     qc, qs, qa, kc, vc, lens = glue.decode_rope_append(qkv, cos, sin, positions, k, v, sk, sv, Hq, Hkv, hd)
-    assert list(lens) == [1, 8, 0, 0]
+    assert list(lens) == [1, 8, S, 0]
     assert np.all(qc[2:] == 0) and np.array_equal(kc[2:], k[2:]) and np.array_equal(vc[2:], v[2:])
     changed = np.zeros_like(k, bool)
     changed[0, :, 0] = changed[1, :, 7] = True
