@@ -71,8 +71,8 @@ struct GemmParams {
     const float* scale_b;
     int out_bf16;
     float* X;  // when set: X[M,N] (fp32) += alpha * A.B^T instead of storing C (the residual-stream update of a decoder block)
-    // SwiGLU mode (BN = 256 only): B holds 128 gate rows then the 128 matching up rows per 256-row tile; the epilogue
-    // writes H[M, F] = silu(alpha*gate) * (alpha*up) as bf16 and reduces max|H| into *amax
+    // SwiGLU mode: B holds 32 gate rows then the 32 matching up rows per 64 rows, so every tile width holds whole
+    // pairs; the epilogue writes H[M, F] = silu(alpha*gate) * (alpha*up) as bf16 and reduces max|H| into *amax
     void* H;
     int F;
     float* amax;
@@ -269,17 +269,17 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
             float tmax = 0.f;  // running max of this thread's row (SwiGLU and e4m3-output modes)
-            if (BN == 256 && p.H) {
-                // gate columns [0,128) and up columns [128,256) of the accumulator -> 128 activations per row
+            if (p.H) {
+                // accumulator columns [64c, 64c+32) are gate and [64c+32, 64c+64) up of activation columns n0/2 + [32c, 32c+32)
                 uint16_t* hrow = reinterpret_cast<uint16_t*>(p.H) + (size_t)row * p.F;
                 const bool hvec_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.H) & 15) == 0);
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < bn / 64; c++) {
                     const int col0 = (n0 >> 1) + c * 32;   // activation column of this chunk
                     if (col0 >= p.F) break;                 // uniform across the CTA
                     uint32_t g[32], uacc[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, g);
-                    tmem_ld_32x32b_x32(taddr + 128 + c * 32, uacc);
+                    tmem_ld_32x32b_x32(taddr + c * 64, g);
+                    tmem_ld_32x32b_x32(taddr + c * 64 + 32, uacc);
                     tmem_ld_wait();
                     uint32_t w[16];
 #pragma unroll
@@ -459,7 +459,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     if (M < 0 || N < 0 || K < 0) return (int)cudaErrorInvalidValue;
     if (M == 0 || N == 0) return 0;
     if (!A || !B || (!C && !X && !H && !D8)) return (int)cudaErrorInvalidValue;
-    if (H && (!amax || F <= 0 || N != 2 * ((F + 127) / 128) * 128 || (reinterpret_cast<uintptr_t>(H) & 1))) return (int)cudaErrorInvalidValue;
+    if (H && (!amax || F <= 0 || N != 2 * ((F + 31) / 32) * 32 || (reinterpret_cast<uintptr_t>(H) & 1))) return (int)cudaErrorInvalidValue;
     if (K == 0 || (K % 16) != 0) return (int)cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
         (reinterpret_cast<uintptr_t>(C) & 1) || (reinterpret_cast<uintptr_t>(X) & 3))
@@ -488,6 +488,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     // Tile width: 256 unless a narrower tile cuts (waves x per-k-block MMA time) by more than a quarter —
     // i.e. only when the 128x256 tiling leaves most SMs idle (small or skinny problems).  Per-k-block MMA
     // time: 128 / 64 / 48 clocks for BN = 256 / 128 / 64 (the last one limited by operand reads).
+    // (For a single row of tiles, choosing the width by the rows of B the busiest SM has to stream instead was
+    // measured and is slower: 16 x 32768 x 8192 62 us against 52 us, 64 x 22016 x 4096 26 us against 19 us.)
     const long long m_tiles = (M + BM - 1) / BM;
     auto estimate = [&](int width, int clocks) {
         const long long tiles = m_tiles * ((N + width - 1) / width);
@@ -495,10 +497,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     };
     int bn = 256;
     long long best = estimate(256, 128) * 3 / 4;
-    if (!H) {  // the SwiGLU epilogue needs gate and up columns of a row in one 256-wide tile
-        if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
-        if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
-    }
+    if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
+    if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
 
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
@@ -516,7 +516,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles >= (1ll << 30)) return (int)cudaErrorInvalidValue;
     const int rem = (int)(tiles % st.num_sms);
-    const bool split_tail = (bn == 256) && !H && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
+    const bool split_tail = (bn == 256) && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
     p.split_from = (int)(split_tail ? tiles - rem : tiles);
     p.num_units = (int)(split_tail ? tiles + rem : tiles);
 
@@ -570,7 +570,7 @@ int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleave
     if (!H || !amax_out || F <= 0) return (int)cudaErrorInvalidValue;
     cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), (cudaStream_t)stream);
     if (e != cudaSuccess) return (int)e;
-    const int n = 2 * ((F + 127) / 128) * 128;
+    const int n = 2 * ((F + 31) / 32) * 32;
     return launch(M, n, K, A, B_interleaved, nullptr, alpha, scale_a, scale_b, 1, (cudaStream_t)stream, nullptr, H, F, amax_out);
 }
 

@@ -108,16 +108,24 @@ def FP8GEMMFP8Out(M, N, K, A, B, D, alpha=1.0, scale_a=0, scale_b=0, scale_d=0, 
 
 
 def interleave_gate_up(w_gate_up, F: int):
-    """[2F, K] (gate rows first) -> the [2*Fp, K] layout fp8_gemm_swiglu reads: per 128 feed-forward columns, the
-    128 gate rows followed by the 128 up rows; rows past F are zero.  Works on torch tensors and numpy arrays."""
-    Fp = (F + 127) // 128 * 128
+    """[2F, K] (gate rows first) -> the [2*Fp, K] layout fp8_gemm_swiglu reads (Fp = F rounded up to 32): per 32
+    feed-forward columns, the 32 gate rows followed by the 32 up rows; rows past F are zero.  Works on torch tensors
+    and numpy arrays."""
+    Fp = (F + 31) // 32 * 32
     K = w_gate_up.shape[1]
-    out = w_gate_up.new_zeros((2 * Fp, K)) if hasattr(w_gate_up, "new_zeros") else __import__("numpy").zeros((2 * Fp, K), w_gate_up.dtype)
-    for t in range(Fp // 128):
-        lo, hi = 128 * t, min(128 * t + 128, F)
-        out[256 * t: 256 * t + (hi - lo)] = w_gate_up[lo:hi]
-        out[256 * t + 128: 256 * t + 128 + (hi - lo)] = w_gate_up[F + lo: F + hi]
-    return out
+    gate, up = w_gate_up[:F], w_gate_up[F:2 * F]
+    if hasattr(w_gate_up, "new_zeros"):
+        out = w_gate_up.new_zeros((Fp // 32, 2, 32, K))
+    else:
+        out = __import__("numpy").zeros((Fp // 32, 2, 32, K), w_gate_up.dtype)
+    full = F // 32
+    if full:
+        out[:full, 0] = gate[:32 * full].reshape(full, 32, K)
+        out[:full, 1] = up[:32 * full].reshape(full, 32, K)
+    if F % 32:
+        out[full, 0, :F % 32] = gate[32 * full:]
+        out[full, 1, :F % 32] = up[32 * full:]
+    return out.reshape(2 * Fp, K)
 
 
 def device_status() -> int:

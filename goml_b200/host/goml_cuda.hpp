@@ -141,7 +141,7 @@ inline void FP8GEMMAccumulateF32(int M, int N, int K, uintptr_t A, uintptr_t B, 
     if (rc != 0) throw Error("fp8_gemm_accumulate_f32: CUDA error " + std::to_string(rc));
 }
 // H (bf16 [M,F]) = silu(g) * u, [g | u] = alpha * (*scaleA) * (*scaleB) * A x Binterleaved^T; max|H| -> *amaxOut.
-// Binterleaved: per 128 feed-forward columns the 128 gate rows then the 128 up rows (InterleaveGateUp below).
+// Binterleaved: per 32 feed-forward columns the 32 gate rows then the 32 up rows (InterleaveGateUp below).
 inline void FP8GEMMSwiGLU(int M, int F, int K, uintptr_t A, uintptr_t Binterleaved, uintptr_t H, float alpha, uintptr_t scaleA,
                           uintptr_t scaleB, uintptr_t amaxOut, uintptr_t stream) {
     const int rc = detail::gemm_lib().swiglu(M, F, K, detail::vp(A), detail::vp(Binterleaved), detail::vp(H), alpha,
@@ -159,16 +159,16 @@ inline void FP8GEMMFP8Out(int M, int N, int K, uintptr_t A, uintptr_t B, uintptr
                                              detail::vp(stream));
     if (rc != 0) throw Error("fp8_gemm_fp8out: CUDA error " + std::to_string(rc));
 }
-// Host-side weight preparation for FP8GEMMSwiGLU: codes [2F, K] (gate rows first) -> [2*Fp, K], Fp = F rounded up to 128.
+// Host-side weight preparation for FP8GEMMSwiGLU: codes [2F, K] (gate rows first) -> [2*Fp, K], Fp = F rounded up to 32:
+// per 32 feed-forward columns the 32 gate rows, then the 32 up rows; rows past F are zero.
 inline std::vector<uint8_t> InterleaveGateUp(const std::vector<uint8_t>& gateUp, int F, int K) {
-    const int Fp = (F + 127) / 128 * 128;
+    const int Fp = (F + 31) / 32 * 32;
     std::vector<uint8_t> out((size_t)2 * Fp * K, 0);
-    for (int t = 0; t < Fp / 128; t++)
-        for (int r = 0; r < 128 && 128 * t + r < F; r++) {
-            std::copy(gateUp.begin() + (size_t)(128 * t + r) * K, gateUp.begin() + (size_t)(128 * t + r + 1) * K, out.begin() + (size_t)(256 * t + r) * K);
-            std::copy(gateUp.begin() + (size_t)(F + 128 * t + r) * K, gateUp.begin() + (size_t)(F + 128 * t + r + 1) * K,
-                      out.begin() + (size_t)(256 * t + 128 + r) * K);
-        }
+    for (int col = 0; col < F; col++) {
+        const size_t dst = (size_t)(64 * (col / 32) + col % 32) * K;
+        std::copy(gateUp.begin() + (size_t)col * K, gateUp.begin() + (size_t)(col + 1) * K, out.begin() + dst);
+        std::copy(gateUp.begin() + (size_t)(F + col) * K, gateUp.begin() + (size_t)(F + col + 1) * K, out.begin() + dst + (size_t)32 * K);
+    }
     return out;
 }
 inline int FP8GEMMDeviceStatus() { return detail::gemm_lib().status(); }

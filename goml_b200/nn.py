@@ -194,7 +194,7 @@ class FP8DecoderBlock:
         BG.DecodeRopeAppend(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), cache.lens.data_ptr(), qc.data_ptr(), qs.data_ptr(),
                             qs.data_ptr() + 4, cache.k.data_ptr(), cache.v.data_ptr(), cache.scales.data_ptr(), cache.scales.data_ptr() + 4,
                             B, H, H, hd, cache.s_max, cache.s_max, seq_lens_out=cache._lens_next.data_ptr(), stream=sh)
-        cache.lens, cache._lens_next = cache._lens_next, cache.lens
+        cache.lens.copy_(cache._lens_next)    # a device copy, not a pointer swap: the step can be replayed from a CUDA graph
         o = torch.empty((B, H, hd), dtype=torch.float16, device=dev)
         self.fa.Decode(qc.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), o.data_ptr(), 0, cache.lens.data_ptr(), B, H, H, hd,
                        cache.s_max, 0, 1.0 / math.sqrt(hd), 1.0, qs.data_ptr(), cache.scales.data_ptr(), cache.scales.data_ptr() + 4, sh)

@@ -2,6 +2,7 @@
 
     python -m goml_b200.run_case fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
     python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
+    python -m goml_b200.run_case blockdec B S D_MODEL H F ITERS  # one decode step of the whole FP8 block against a cache of S keys
     python -m goml_b200.run_case decstep B HQ HKV S D ITERS    # new token's RoPE + quantise + cache append, then fa_decode
     python -m goml_b200.run_case gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
     python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
@@ -123,6 +124,58 @@ def main(argv):
         us = e0.elapsed_time(e1) / iters * 1e3
         nbytes = 2 * B * hkv * S * D
         print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}{f' page={page}' if page else ''}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
+    elif kind == "blockdec":
+        # one decode step of the whole block (one new token per sequence) against a cache of S keys per sequence
+        from . import nn
+        B, S, d, H, Fh, iters = args
+        g = torch.Generator(device="cuda").manual_seed(4)
+        rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device="cuda") * std
+        blk = nn.FP8DecoderBlock(d, H, Fh, rn(3 * d, d), rn(d, d), rn(2 * Fh, d), rn(d, Fh), torch.ones(d, device="cuda"), torch.ones(d, device="cuda"))
+        cache = nn.FP8KVCache(B, H, S + 2 * iters + 16, d // H)
+        cache.k[:, :, :S].copy_(torch.randn(B, H, S, d // H, generator=g, device="cuda").to(torch.float8_e4m3fn).view(torch.uint8))
+        cache.v[:, :, :S].copy_(torch.randn(B, H, S, d // H, generator=g, device="cuda").to(torch.float8_e4m3fn).view(torch.uint8))
+        cache.lens.fill_(S)
+        x = rn(B, d, std=1.0)
+        for _ in range(3):
+            y = blk.decode_step(x, cache)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            y = blk.decode_step(x, cache)
+        e1.record()
+        torch.cuda.synchronize()
+        blk.fa.DeviceStatus()
+        assert G.device_status() == 0 and bool(torch.isfinite(y).all()) and int(cache.lens[0]) == S + 3 + iters
+        us = e0.elapsed_time(e1) / iters * 1e3
+        nbytes = d * (3 * d + d + 3 * Fh) + 2 * B * H * S * (d // H)          # weights once + the K and V cache once
+        print(f"block decode step B={B} cache S={S} d={d} H={H} F={Fh}: {us:8.1f} us per step, {nbytes / us / 1e3:6.0f} GB/s "
+              f"of weights + cache ({nbytes / 1e6:.0f} MB)")
+        # the same step captured once in a CUDA graph and replayed: the ~20 launches of a step cost no host time
+        cache.lens.fill_(S)
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            blk.decode_step(x, cache)                                          # warm-up on the capture stream
+            side.synchronize()
+            cache.lens.fill_(S)
+            with torch.cuda.graph(graph, stream=side):
+                yg = blk.decode_step(x, cache)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        blk.fa.DeviceStatus()
+        assert G.device_status() == 0 and bool(torch.isfinite(yg).all()) and int(cache.lens[0]) == S + 2 + iters
+        usg = e0.elapsed_time(e1) / iters * 1e3
+        print(f"block decode step B={B} cache S={S} replayed from a CUDA graph: {usg:8.1f} us per step, {nbytes / usg / 1e3:6.0f} GB/s")
+        blk.close()
     elif kind == "decstep":
         # one decode step's attention part: RoPE + quantise + cache append of the new token, then fa_decode
         from . import block_glue as BG

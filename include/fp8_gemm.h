@@ -68,8 +68,9 @@ FP8GEMM_API int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, cons
  *   H[M,F] (bf16) = silu(g) * u,   g = s * A . Wgate^T,   u = s * A . Wup^T,   s = alpha * (*scale_a) * (*scale_b)
  * (silu(x) = x / (1 + e^-x); nn/feedforward.go:54-79 computes W2(silu(W1 x) * W3 x)), and max|H| reduced into
  * *amax_out (cleared by the call) for the per-tensor quantiser of the down projection's operand.
- * B_interleaved holds both weights, [2 * Fp, K] with Fp = F rounded up to 128: rows [256t, 256t+128) are rows
- * [128t, 128t+128) of Wgate, rows [256t+128, 256t+256) the same rows of Wup; rows past F are zero.
+ * B_interleaved holds both weights, [2 * Fp, K] with Fp = F rounded up to 32: rows [64t, 64t+32) are rows
+ * [32t, 32t+32) of Wgate, rows [64t+32, 64t+64) the same rows of Wup; rows past F are zero (every tile width the
+ * kernel uses, 64 to 256 columns, then holds whole gate/up pairs, so small M runs on narrow tiles).
  * The 16-bit gate/up matrix is never written. */
 FP8GEMM_API int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* B_interleaved, void* H, float alpha,
                                 const float* scale_a, const float* scale_b, float* amax_out, void* stream);

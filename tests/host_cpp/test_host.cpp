@@ -67,14 +67,16 @@ static int run_cpu(const char* libs_dir) {
     CHECK(thrown([] { FP8GEMMSwiGLU(8, 0, 32, 16, 16, 16, 1.0f, 0, 0, 16, 0); }) == "fp8_gemm_swiglu: CUDA error 1");
     CHECK(thrown([] { FP8GEMMFP8Out(8, 8, 32, 16, 16, 0, 1.0f, 0, 0, 0, 0, 0); }) == "fp8_gemm_fp8out: CUDA error 1");
     CHECK(thrown([] { fp8_decode_append_args_t a{}; a.batch = 1; DecodeRopeAppend(a); }) == "fp8_decode_rope_append: CUDA error 1");
-    {   // weight layout for the SwiGLU GEMM: F = 130 -> two column blocks, the second one mostly padding
-        const int F = 130, K = 4;
+    {   // weight layout for the SwiGLU GEMM: F = 70 -> three blocks of 32 columns, the last one mostly padding
+        const int F = 70, K = 4;
         std::vector<uint8_t> w((size_t)2 * F * K);
         for (size_t i = 0; i < w.size(); i++) w[i] = (uint8_t)(i / K + 1);   // row index + 1 in every byte of a row
         const auto wi = InterleaveGateUp(w, F, K);
-        CHECK(wi.size() == (size_t)2 * 256 * K);
-        CHECK(wi[0] == 1 && wi[(size_t)127 * K] == 128 && wi[(size_t)128 * K] == (uint8_t)(F + 1) && wi[(size_t)256 * K] == 129 &&
-              wi[(size_t)257 * K] == 130 && wi[(size_t)258 * K] == 0 && wi[(size_t)384 * K] == (uint8_t)(F + 129) && wi[(size_t)386 * K] == 0);
+        CHECK(wi.size() == (size_t)2 * 96 * K);
+        // rows 0..31 gate 0..31, rows 32..63 up 0..31, rows 64..95 gate 32..63, ..., rows 128..133 gate 64..69, then zeros
+        CHECK(wi[0] == 1 && wi[(size_t)31 * K] == 32 && wi[(size_t)32 * K] == (uint8_t)(F + 1) && wi[(size_t)64 * K] == 33 &&
+              wi[(size_t)128 * K] == 65 && wi[(size_t)133 * K] == 70 && wi[(size_t)134 * K] == 0 &&
+              wi[(size_t)160 * K] == (uint8_t)(F + 65) && wi[(size_t)166 * K] == 0);
     }
     return fails;
 }
