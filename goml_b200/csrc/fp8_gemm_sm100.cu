@@ -82,7 +82,10 @@ struct GemmParams {
     int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
     int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
-    int num_units;   // split_from + 2 * (number of split tiles)
+    int num_units;   // split_from + 2 * (number of split tiles); with ksplit > 1: tiles * ksplit
+    // split-K (accumulate mode through TMA reduce only, where partial sums may simply be added into X): unit u is
+    // slice u % ksplit of tile u / ksplit and covers pipeline stages [slice * ks_per, min((slice + 1) * ks_per, all))
+    int ksplit, ks_per;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
@@ -191,9 +194,10 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             bool ok = true;
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 int tm, n0, bn;
-                unit_coords<BN>(u, p, tm, n0, bn);
+                const int t = u / p.ksplit, ks0 = (u - t * p.ksplit) * p.ks_per, ks1 = min(ks0 + p.ks_per, k_stages);
+                unit_coords<BN>(t, p, tm, n0, bn);
                 const CUtensorMap* tb = (bn == BN) ? &tmap_b : &tmap_b_half;
-                for (int ks = 0; ks < k_stages; ks++) {
+                for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
                     mbar_arrive_expect_tx(fb, KSUB * (A_BYTES + bn * BK));
@@ -218,13 +222,14 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             int buf = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-                const bool whole = !(BN == 256 && u >= p.split_from);
+                const int t = u / p.ksplit, ks0 = (u - t * p.ksplit) * p.ks_per, ks1 = min(ks0 + p.ks_per, k_stages);
+                const bool whole = !(BN == 256 && t >= p.split_from);
                 const uint32_t idesc = whole ? make_idesc_e4m3_f32(BM, BN, 0, 0) : make_idesc_e4m3_f32(BM, BN / 2, 0, 0);
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_MMA)) break;
                 tphase[buf] ^= 1;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int ks = 0; ks < k_stages; ks++) {
+                for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -235,7 +240,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                         for (int k = 0; k < BK / 32; k++) {
                             // +32 bytes along K inside the swizzle span = +2 in the address field
-                            mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | sub | k) != 0);
+                            mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
                         }
                     }
                     mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
@@ -261,7 +266,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         int sbuf = 0;  // staging box in use (accumulate mode)
         for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
             int tm, n0, bn;
-            unit_coords<BN>(u, p, tm, n0, bn);
+            unit_coords<BN>(u / p.ksplit, p, tm, n0, bn);
             if (!mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_EPILOGUE)) break;
             tphase[buf] ^= 1;
             tc_fence_after();
@@ -446,6 +451,8 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
 // ---------------------------------------------------------------- host side
 
+constexpr int Tile_KSUB(int bn) { return bn == 256 ? Tile<256>::KSUB : bn == 128 ? Tile<128>::KSUB : Tile<64>::KSUB; }
+
 struct DeviceState {
     bool ready = false;
     int num_sms = 0;
@@ -519,6 +526,21 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     const bool split_tail = (bn == 256) && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
     p.split_from = (int)(split_tail ? tiles - rem : tiles);
     p.num_units = (int)(split_tail ? tiles + rem : tiles);
+    // Split-K: a problem with fewer tiles than half the SMs and a long K (the O and down projections of a decode
+    // step: 16 x 4096 x 11008 is 64 tiles) leaves most SMs idle while each busy one streams a long panel of B.
+    // Where the result is added into X by TMA reduce anyway, slices of K go to different CTAs and each adds its
+    // partial sum (the order of those fp32 additions is then not fixed from run to run).
+    const int k_stages = (p.k_blocks + Tile_KSUB(bn) - 1) / Tile_KSUB(bn);
+    p.ksplit = 1;
+    if (p.x_tma && !split_tail && 2 * tiles <= st.num_sms) {
+        long long ks = st.num_sms / tiles;
+        if (ks > k_stages / 4) ks = k_stages / 4;   // at least four pipeline stages of work per slice
+        if (ks > 8) ks = 8;
+        if (ks > 1) p.ksplit = (int)ks;
+    }
+    p.ks_per = (k_stages + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (k_stages + p.ks_per - 1) / p.ks_per;   // no empty slice
+    p.num_units *= p.ksplit;
 
     CUtensorMap ta, tb, tbh;
     if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||

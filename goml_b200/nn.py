@@ -151,7 +151,7 @@ class FP8DecoderBlock:
         dev, T, d, H, hd, Fh = x.device, B * S, self.d, self.H, self.hd, self.F
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
-        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        sa = lambda n=2: torch.empty(n, dtype=torch.float32, device=dev)   # scale and amax words: every entry point clears its own amax
         h = x.float().clone()                                   # residual stream, updated in place
         rstd = torch.empty(T, dtype=torch.float32, device=dev)
         cos, sin = self.rope_tables(S, dev)
@@ -182,7 +182,7 @@ class FP8DecoderBlock:
         assert (B, H, hd) == (cache.B, cache.H, cache.hd)
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
-        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        sa = lambda n=2: torch.empty(n, dtype=torch.float32, device=dev)
         h = x.float().clone()
         rstd = torch.empty(B, dtype=torch.float32, device=dev)
         cos, sin = self.rope_tables(cache.s_max, dev)
@@ -208,7 +208,7 @@ class FP8DecoderBlock:
         dev, d, Fh = h.device, self.d, self.F
         sh = torch.cuda.current_stream().cuda_stream
         u8 = lambda *shape: torch.empty(shape, dtype=torch.uint8, device=dev)
-        sa = lambda n=2: torch.zeros(n, dtype=torch.float32, device=dev)
+        sa = lambda n=2: torch.empty(n, dtype=torch.float32, device=dev)
         rstd = torch.empty(T, dtype=torch.float32, device=dev)
         xq2 = FP8Tensor(u8(T, d), sa())
         BG.RMSNormQuantize(h.data_ptr(), 0, 0, self.norm2.data_ptr(), xq2.codes.data_ptr(), xq2.sa.data_ptr(),

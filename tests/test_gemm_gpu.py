@@ -123,7 +123,8 @@ def test_config2_full_size_on_sampled_rows(cuda, built_libs):
     assert torch.equal(c3, c[perm])
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 144), (129, 257, 160), (16, 8192, 256)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (300, 520, 144), (129, 257, 160), (16, 8192, 256),
+                                   (16, 4096, 4096), (48, 1024, 11008), (16, 512, 2064)])      # the last three run split over K
 def test_accumulate_into_fp32(cuda, built_libs, M, N, K):
     # the residual-stream update in the epilogue: X += alpha * sa * sb * A.B^T, fp32 accumulators added un-rounded
     from goml_b200 import fp8_gemm as G
