@@ -274,7 +274,10 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + (size_t)row * p.N;
             float tmax = 0.f;  // running max of this thread's row (SwiGLU and e4m3-output modes)
-            if (p.H) {
+            if (tm * BM + quad * 32 >= p.M) {
+                // all 32 rows of this warp lie past M (a skinny problem uses 16 of a tile's 128 rows): nothing to
+                // read, convert or store; the accumulator buffer is handed back below as usual
+            } else if (p.H) {
                 // accumulator columns [64c, 64c+32) are gate and [64c+32, 64c+64) up of activation columns n0/2 + [32c, 32c+32)
                 uint16_t* hrow = reinterpret_cast<uint16_t*>(p.H) + (size_t)row * p.F;
                 const bool hvec_ok = (p.F % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.H) & 15) == 0);
