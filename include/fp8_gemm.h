@@ -60,7 +60,9 @@ FP8GEMM_API int fp8_gemm_scaled(int M, int N, int K, const void* A, const void* 
  *   X[M,N] (fp32, row-major) += (alpha * (*scale_a) * (*scale_b)) * A . B^T
  * read-modify-write with 128-bit accesses; takes the place of a 16-bit result followed by
  * a separate add pass over X (x = x + W y in internal/abjexam/llama_hf_f64ref.go:150,178).
- * The fp32 accumulators are added un-rounded. */
+ * The fp32 accumulators are added un-rounded.  A problem with few output tiles and a long K (M <= 128 rows against a
+ * wide weight) is divided over K among several thread blocks, each adding its partial sum into X: the result is then
+ * the same sum in an order that is not fixed from run to run (differences in the last bits of fp32). */
 FP8GEMM_API int fp8_gemm_accumulate_f32(int M, int N, int K, const void* A, const void* B, float* X, float alpha,
                                         const float* scale_a, const float* scale_b, void* stream);
 
