@@ -63,6 +63,10 @@ enum : uint32_t {
 
 __device__ uint32_t g_gemm_status = 0;  // first non-zero code any CTA reported (per device)
 
+#ifndef FP8_GEMM_C_TMA
+#define FP8_GEMM_C_TMA 1
+#endif
+
 struct GemmParams {
     int M, N, K;
     void* C;
@@ -79,6 +83,7 @@ struct GemmParams {
     // e4m3-output mode: D8[M,N] = e4m3(scale_d * v), v = alpha * A.B^T rounded to fp32, and max|v| reduced into *amax
     uint8_t* D8;
     const float* scale_d;
+    int c_tma;  // C (16-bit) can be described by a tensor map (16-byte aligned, N % 8 == 0): tiles leave through staging + TMA store
     int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
     int split_from;  // tiles [split_from, m_tiles*n_tiles) of the last, less than half full wave run as two half-width units each
@@ -318,6 +323,41 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         }
                     }
                 }
+            } else if (FP8_GEMM_C_TMA && p.c_tma) {
+                // 16-bit C through the memory system: two 32-column chunks of this warp's 32 rows fill one 32 x 64 box
+                // (128-byte rows, swizzled like the fp32 boxes of the accumulate mode), one TMA store per box,
+                // double-buffered; rows >= M and columns >= N are clipped by the tensor map
+#pragma unroll 1
+                for (int c2 = 0; c2 < bn / 64; c2++) {
+                    const int col0 = n0 + c2 * 64;
+                    if (col0 >= p.N) break;  // uniform across the CTA
+                    const uint32_t box = staging + (quad * 2 + sbuf) * STAGING_BOX;
+                    if (lane == 0) tma_store_wait_read<1>();  // the store that used this buffer two boxes ago has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        uint32_t acc[32];
+                        tmem_ld_32x32b_x32(taddr + c2 * 64 + hf * 32, acc);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            const uint32_t dst = box + lane * 128 + (((hf * 4 + v) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                         "r"(pack_out(__uint_as_float(acc[8 * v + 0]) * alpha, __uint_as_float(acc[8 * v + 1]) * alpha, p.out_bf16)),
+                                         "r"(pack_out(__uint_as_float(acc[8 * v + 2]) * alpha, __uint_as_float(acc[8 * v + 3]) * alpha, p.out_bf16)),
+                                         "r"(pack_out(__uint_as_float(acc[8 * v + 4]) * alpha, __uint_as_float(acc[8 * v + 5]) * alpha, p.out_bf16)),
+                                         "r"(pack_out(__uint_as_float(acc[8 * v + 6]) * alpha, __uint_as_float(acc[8 * v + 7]) * alpha, p.out_bf16))
+                                         : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_x, box, col0, tm * BM + quad * 32);
+                        tma_store_commit();
+                    }
+                    sbuf ^= 1;
+                }
             } else
 #pragma unroll 1
             for (int c = 0; c < bn / 32; c++) {
@@ -431,7 +471,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
             }
         }
-        if (p.X && p.x_tma && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
+        if (((p.X && p.x_tma) || (FP8_GEMM_C_TMA && p.c_tma)) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
 
     // ------------------------------------------------------------- teardown
@@ -517,6 +557,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.H = H; p.F = F; p.amax = amax;
     p.D8 = D8; p.scale_d = scale_d;
     p.x_tma = (X && (N % 4) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) ? 1 : 0;
+    p.c_tma = (C && !X && !H && !D8 && (N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
     p.m_tiles = (int)m_tiles;
     p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
@@ -553,6 +594,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
 
     CUtensorMap tx = ta;  // placeholder when there is nothing to describe
     if (p.x_tma && !make_tmap_f32_2d(&tx, X, (uint64_t)M, (uint64_t)N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
+    if (p.c_tma && !make_tmap_u16_2d(&tx, C, (uint64_t)M, (uint64_t)N, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
 
     const int grid = (int)(p.num_units < st.num_sms ? p.num_units : st.num_sms);
     if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);

@@ -91,4 +91,20 @@ inline bool make_tmap_f32_2d(CUtensorMap* m, const void* base, uint64_t rows, ui
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 2-D map over a dense row-major matrix of 16-bit elements [rows, cols] (fp16 or bf16: the copy does not interpret
+// them); box = [box_rows, box_cols].  cols * 2 must be a multiple of 16 and base 16-byte aligned.  Used by TMA
+// stores of an output tile (parts of a box outside the matrix are not written).
+inline bool make_tmap_u16_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                             uint32_t box_cols, CUtensorMapSwizzle swz) {
+    encode_tiled_fn enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace sm100
