@@ -83,6 +83,8 @@ struct GemmParams {
     // e4m3-output mode: D8[M,N] = e4m3(scale_d * v), v = alpha * A.B^T rounded to fp32, and max|v| reduced into *amax
     uint8_t* D8;
     const float* scale_d;
+    int h_tma;  // SwiGLU output H likewise (F % 8 == 0); only tiles of 128 or 256 columns use it
+    int d_tma;  // e4m3 output D likewise (N % 16 == 0); only tiles of 128 or 256 columns use it
     int c_tma;  // C (16-bit) can be described by a tensor map (16-byte aligned, N % 8 == 0): tiles leave through staging + TMA store
     int x_tma;  // X can be described by a tensor map (16-byte aligned, N % 4 == 0): add through TMA reduce, else read-modify-write
     int m_tiles, n_tiles, k_blocks;
@@ -311,7 +313,31 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         // max of the rounded values = what the quantiser that follows will see
                         tmax = fmaxf(tmax, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xffff0000u))));
                     }
-                    if (row < p.M) {
+                    if (BN >= 128 && p.h_tma) {
+                        // two 32-column chunks fill one 32 x 64 box of this warp's rows (every tile and half-tile is a
+                        // whole number of boxes; past column F the tensor map clips), one TMA store per box
+                        const uint32_t box = staging + (quad * 2 + sbuf) * STAGING_BOX;
+                        if ((c & 1) == 0) {
+                            if (lane == 0) tma_store_wait_read<1>();  // the store that used this buffer two boxes ago has read it
+                            __syncwarp();
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            const uint32_t dst = box + lane * 128 + ((((c & 1) * 4 + v) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * v]), "r"(w[4 * v + 1]), "r"(w[4 * v + 2]),
+                                         "r"(w[4 * v + 3])
+                                         : "memory");
+                        }
+                        if ((c & 1) || col0 + 32 >= p.F) {   // box complete, or no further chunk of this matrix
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(&tmap_x, box, col0 - (c & 1) * 32, tm * BM + quad * 32);
+                                tma_store_commit();
+                            }
+                            sbuf ^= 1;
+                        }
+                    } else if (row < p.M) {
                         if (hvec_ok && col0 + 32 <= p.F) {
                             uint4* dst = reinterpret_cast<uint4*>(hrow + col0);
 #pragma unroll
@@ -322,6 +348,46 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                                 if (col0 + j < p.F) hrow[col0 + j] = (uint16_t)((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
                         }
                     }
+                }
+            } else if (BN >= 128 && p.d_tma) {
+                // e4m3 D through the memory system: four 32-column chunks of this warp's 32 rows fill one 32 x 128 box
+#pragma unroll 1
+                for (int c4 = 0; c4 < bn / 128; c4++) {
+                    const int col0 = n0 + c4 * 128;
+                    if (col0 >= p.N) break;  // uniform across the CTA
+                    const uint32_t box = staging + (quad * 2 + sbuf) * STAGING_BOX;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        uint32_t acc[32];
+                        tmem_ld_32x32b_x32(taddr + c4 * 128 + q4 * 32, acc);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            v[j] = __uint_as_float(acc[j]) * alpha;
+                            tmax = fmaxf(tmax, fabsf(v[j]));   // columns >= N and rows >= M hold zeros
+                            v[j] *= scale_d;
+                        }
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint32_t dst = box + lane * 128 + (((q4 * 2 + h) ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                         "r"(pack_e4m3x4(v[16 * h + 0], v[16 * h + 1], v[16 * h + 2], v[16 * h + 3])),
+                                         "r"(pack_e4m3x4(v[16 * h + 4], v[16 * h + 5], v[16 * h + 6], v[16 * h + 7])),
+                                         "r"(pack_e4m3x4(v[16 * h + 8], v[16 * h + 9], v[16 * h + 10], v[16 * h + 11])),
+                                         "r"(pack_e4m3x4(v[16 * h + 12], v[16 * h + 13], v[16 * h + 14], v[16 * h + 15]))
+                                         : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_x, box, col0, tm * BM + quad * 32);
+                        tma_store_commit();
+                    }
+                    sbuf ^= 1;
                 }
             } else if (FP8_GEMM_C_TMA && p.c_tma) {
                 // 16-bit C through the memory system: two 32-column chunks of this warp's 32 rows fill one 32 x 64 box
@@ -471,7 +537,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
             }
         }
-        if (((p.X && p.x_tma) || (FP8_GEMM_C_TMA && p.c_tma)) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
+        if (((p.X && p.x_tma) || (FP8_GEMM_C_TMA && p.c_tma) || p.h_tma || p.d_tma) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
 
     // ------------------------------------------------------------- teardown
@@ -558,6 +624,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.D8 = D8; p.scale_d = scale_d;
     p.x_tma = (X && (N % 4) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) ? 1 : 0;
     p.c_tma = (C && !X && !H && !D8 && (N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+    p.h_tma = (H && bn >= 128 && (F % 8) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) ? 1 : 0;
+    p.d_tma = (D8 && !H && !X && bn >= 128 && (N % 16) == 0 && (reinterpret_cast<uintptr_t>(D8) & 15) == 0) ? 1 : 0;
     p.m_tiles = (int)m_tiles;
     p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
@@ -595,6 +663,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     CUtensorMap tx = ta;  // placeholder when there is nothing to describe
     if (p.x_tma && !make_tmap_f32_2d(&tx, X, (uint64_t)M, (uint64_t)N, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
     if (p.c_tma && !make_tmap_u16_2d(&tx, C, (uint64_t)M, (uint64_t)N, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
+    if (p.h_tma && !make_tmap_u16_2d(&tx, H, (uint64_t)M, (uint64_t)F, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
+    if (p.d_tma && !make_tmap_u8_2d(&tx, D8, (uint64_t)M, (uint64_t)N, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
 
     const int grid = (int)(p.num_units < st.num_sms ? p.num_units : st.num_sms);
     if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);

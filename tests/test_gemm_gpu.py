@@ -145,7 +145,8 @@ def test_accumulate_into_fp32(cuda, built_libs, M, N, K):
     assert np.abs(got - ref).max() <= 1e-5 * max(rms, 1.0) * np.sqrt(K), np.abs(got - ref).max()
 
 
-@pytest.mark.parametrize("M,F,K", [(256, 1376, 512), (130, 704, 256), (64, 11008, 128), (300, 128, 144)])
+@pytest.mark.parametrize("M,F,K", [(256, 1376, 512), (130, 704, 256), (64, 11008, 128), (300, 128, 144),
+                                   (2048, 2440, 128), (520, 4096, 256)])     # wide tiles: H leaves through TMA stores, clipped at column F
 def test_swiglu_epilogue(cuda, built_libs, M, F, K):
     # gate/up projections with silu(gate) * up in the epilogue: bf16 H, max|H| exact, and the quantiser pass that follows
     from goml_b200 import fp8_gemm as G, block_glue as BG
@@ -189,7 +190,8 @@ def _fp8out(a, b, alpha, sa, sb, sd, want_amax=True, guard=0):
     return d.cpu().numpy(), float(s[3].item())
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 512, 512), (130, 272, 144), (129, 250, 160), (16, 8192, 256), (300, 24, 1024)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 512), (130, 272, 144), (129, 250, 160), (16, 8192, 256), (300, 24, 1024),
+                                   (2048, 4880, 128), (520, 4096, 256)])     # wide tiles: D leaves through TMA stores, clipped at column N
 def test_fp8out_exact_on_integer_data(cuda, built_libs, M, N, K):
     # small-integer operands: every partial sum is exact in fp32, so the e4m3 codes and amax must be bit-exact
     rng = np.random.default_rng(M * 7 + N)
