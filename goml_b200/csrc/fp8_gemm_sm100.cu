@@ -93,6 +93,10 @@ struct GemmParams {
     // split-K (accumulate mode through TMA reduce only, where partial sums may simply be added into X): unit u is
     // slice u % ksplit of tile u / ksplit and covers pipeline stages [slice * ks_per, min((slice + 1) * ks_per, all))
     int ksplit, ks_per;
+    // rows of A one TMA box brings in: 128, or for a single row of tiles with M <= 64 the next of 16 / 32 / 64, so a
+    // skinny problem does not fill shared memory with 128-row tiles of mostly zero padding; the tile rows past it
+    // keep whatever shared memory held (their accumulator rows are never stored or counted)
+    int a_rows;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& tm, int& tn) {
@@ -207,7 +211,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(fb, KSUB * (A_BYTES + bn * BK));
+                    mbar_arrive_expect_tx(fb, KSUB * (p.a_rows * BK + bn * BK));
 #pragma unroll
                     for (int sub = 0; sub < KSUB; sub++) {
                         // a k-block past the end of K (odd count) is a fully out-of-range box: zero-filled, bytes still counted
@@ -531,7 +535,8 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
             buf ^= 1;
             if (p.amax) {
-                // rows >= M and columns past the matrix hold zeros (zero-filled operand rows): they never raise the maximum
+                if (row >= p.M) tmax = 0.f;   // rows past M may hold anything when A is loaded with a short box
+                // columns past the matrix hold zeros (zero-filled operand rows): they never raise the maximum
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
                 if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
@@ -654,8 +659,10 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.ksplit = (k_stages + p.ks_per - 1) / p.ks_per;   // no empty slice
     p.num_units *= p.ksplit;
 
+    p.a_rows = BM;
+    if (m_tiles == 1 && M <= 64) p.a_rows = M <= 16 ? 16 : M <= 32 ? 32 : 64;
     CUtensorMap ta, tb, tbh;
-    if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+    if (!make_tmap_u8_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint32_t)p.a_rows, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_tmap_u8_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint32_t)bn, BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_tmap_u8_2d(&tbh, B, (uint64_t)N, (uint64_t)K, (uint32_t)(bn == 256 ? 128 : bn), BK, CU_TENSOR_MAP_SWIZZLE_128B))
         return (int)cudaErrorInvalidValue;
