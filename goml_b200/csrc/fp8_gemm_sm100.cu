@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/fp8_gemm.h"
 #include "sm100_ptx.cuh"
@@ -41,15 +42,16 @@ constexpr int STAGING_BYTES = 4 * 2 * STAGING_BOX;
 // 128 B/clk shared-memory read rate only for BN >= 128); 128 and 64 exist so that small and
 // skinny problems (few 128x256 tiles) still spread over all SMs — those are HBM/latency-bound,
 // and a narrower tile leaves room for a deeper TMA ring.
-template <int BN>
+// MT = 2: a CTA works on a pair of vertically adjacent tiles (256 rows) that share every B tile it loads.
+template <int BN, int MT = 1>
 struct Tile {
     static constexpr int B_BYTES = BN * BK;
     // The narrow tile serves HBM-bound problems whose MMAs take only 192 clk per k-block: there the producer's and the
     // issuer's per-stage work (a wait, an expect / a commit) is the bound, so a stage holds two k-blocks.
     static constexpr int KSUB = (BN == 64) ? 2 : 1;
-    static constexpr int SUB_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SUB_BYTES = MT * A_BYTES + B_BYTES;
     static constexpr int STAGE_BYTES = KSUB * SUB_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 4;
+    static constexpr int STAGES = (MT == 2) ? 3 : (BN == 256) ? 4 : (BN == 128) ? 6 : 4;
     static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers (a power of two >= 32)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -145,16 +147,16 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
     return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-template <int BN>
+template <int BN, int MT = 1>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_b_half, const __grid_constant__ CUtensorMap tmap_x,
                         const GemmParams p) {
-    constexpr int STAGES = Tile<BN>::STAGES;
-    constexpr int STAGE_BYTES = Tile<BN>::STAGE_BYTES;
-    constexpr int TMEM_COLS = Tile<BN>::TMEM_COLS;
-    constexpr int KSUB = Tile<BN>::KSUB;
-    constexpr int SUB_BYTES = Tile<BN>::SUB_BYTES;
+    constexpr int STAGES = Tile<BN, MT>::STAGES;
+    constexpr int STAGE_BYTES = Tile<BN, MT>::STAGE_BYTES;
+    constexpr int TMEM_COLS = Tile<BN, MT>::TMEM_COLS;
+    constexpr int KSUB = Tile<BN, MT>::KSUB;
+    constexpr int SUB_BYTES = Tile<BN, MT>::SUB_BYTES;
     const int k_stages = (p.k_blocks + KSUB - 1) / KSUB;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle atom = 8 rows x 128 B)
@@ -211,14 +213,15 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(fb, KSUB * (p.a_rows * BK + bn * BK));
+                    mbar_arrive_expect_tx(fb, KSUB * (MT * p.a_rows * BK + bn * BK));
 #pragma unroll
                     for (int sub = 0; sub < KSUB; sub++) {
                         // a k-block past the end of K (odd count) is a fully out-of-range box: zero-filled, bytes still counted
                         const int kb = ks * KSUB + sub;
                         const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
-                        tma_load_2d(sa, &tmap_a, fb, kb * BK, tm * BM);
-                        tma_load_2d(sa + A_BYTES, tb, fb, kb * BK, n0);
+                        tma_load_2d(sa, &tmap_a, fb, kb * BK, MT * tm * BM);
+                        if (MT == 2) tma_load_2d(sa + A_BYTES, &tmap_a, fb, kb * BK, (2 * tm + 1) * BM);   // past M: zero-filled
+                        tma_load_2d(sa + MT * A_BYTES, tb, fb, kb * BK, n0);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -236,6 +239,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const int t = u / p.ksplit, ks0 = (u - t * p.ksplit) * p.ks_per, ks1 = min(ks0 + p.ks_per, k_stages);
                 const bool whole = !(BN == 256 && t >= p.split_from);
                 const uint32_t idesc = whole ? make_idesc_e4m3_f32(BM, BN, 0, 0) : make_idesc_e4m3_f32(BM, BN / 2, 0, 0);
+                if (MT == 2) buf = 0;   // a tile pair takes both accumulator buffers: upper half in 0, lower half in 1
                 if (!mbar_wait(bar_tempty + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_MMA)) break;
                 tphase[buf] ^= 1;
                 tc_fence_after();
@@ -247,17 +251,33 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     for (int sub = 0; sub < KSUB; sub++) {
                         const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
                         const uint64_t adesc = kmajor_desc_sw128(sa);
-                        const uint64_t bdesc = kmajor_desc_sw128(sa + A_BYTES);
+                        const uint64_t bdesc = kmajor_desc_sw128(sa + MT * A_BYTES);
 #pragma unroll
                         for (int k = 0; k < BK / 32; k++) {
                             // +32 bytes along K inside the swizzle span = +2 in the address field
                             mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
                         }
+                        if (MT == 2) {
+                            // lower half of the pair: the other accumulator buffer, the same B operand.  Its buffer is
+                            // waited for only here, so the epilogue of the previous pair's lower half overlaps the
+                            // first MMAs of this pair's upper half.
+                            if (ks == ks0 && sub == 0) {
+                                if (!mbar_wait(bar_tempty + 8, tphase[1], abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                                tphase[1] ^= 1;
+                                tc_fence_after();
+                            }
+                            const uint64_t adesc2 = kmajor_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                            for (int k = 0; k < BK / 32; k++)
+                                mma_f8f6f4_ss(tmem_base + BN, adesc2 + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
+                        }
                     }
+                    if (!ok) break;
                     mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) mma_commit(bar_tfull + 8 * buf);  // accumulator complete
+                if (ok && MT == 2) mma_commit(bar_tfull + 8);
                 buf ^= 1;
             }
         }
@@ -275,10 +295,12 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         uint32_t tphase[2] = {0, 0};
         int buf = 0;
         int sbuf = 0;  // staging box in use (accumulate mode)
-        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x)
+        for (int hsel = 0; hsel < MT; hsel++) {   // a tile pair is two tiles to the epilogue: buffer 0, then buffer 1
             int tm, n0, bn;
             unit_coords<BN>(u / p.ksplit, p, tm, n0, bn);
-            if (!mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_EPILOGUE)) break;
+            tm = MT * tm + hsel;
+            if (!mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, ST_TIMEOUT_EPILOGUE)) goto epilogue_done;
             tphase[buf] ^= 1;
             tc_fence_after();
             const int row = tm * BM + row_in_tile;
@@ -542,6 +564,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), __float_as_uint(tmax));
             }
         }
+    epilogue_done:
         if (((p.X && p.x_tma) || (FP8_GEMM_C_TMA && p.c_tma) || p.h_tma || p.d_tma) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
 
@@ -598,6 +621,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
         if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Tile<256>::SMEM_BYTES)) != cudaSuccess) return (int)e;
+        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<256, 2>::SMEM_BYTES)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Tile<128>::SMEM_BYTES)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -621,6 +646,12 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     if (estimate(128, 64) < best) { best = estimate(128, 64); bn = 128; }
     if (estimate(64, 48) < best) { best = estimate(64, 48); bn = 64; }
 
+    // Tile pairs: with at least two waves of 256 x 256 pairs and a K long enough to amortise the three-stage ring, a
+    // CTA holds two vertically adjacent 128 x 256 accumulators (both TMEM buffers) and feeds both from each B tile it
+    // loads: 32 KB instead of 48 KB of operands per 128 x 256 x 128 block of MMA work (8192^3: 2739 -> 2965 TFLOP/s).
+    // FP8_GEMM_NO_PAIR in the environment keeps single tiles (the parity tests compare the two, bit for bit).
+    const bool pair = (bn == 256) && K >= 2048 && m_tiles >= 2 && !getenv("FP8_GEMM_NO_PAIR") &&
+                      ((m_tiles + 1) / 2) * ((N + 255) / 256) >= 2ll * st.num_sms;
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
@@ -631,7 +662,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     p.c_tma = (C && !X && !H && !D8 && (N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
     p.h_tma = (H && bn >= 128 && (F % 8) == 0 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) ? 1 : 0;
     p.d_tma = (D8 && !H && !X && bn >= 128 && (N % 16) == 0 && (reinterpret_cast<uintptr_t>(D8) & 15) == 0) ? 1 : 0;
-    p.m_tiles = (int)m_tiles;
+    p.m_tiles = (int)(pair ? (m_tiles + 1) / 2 : m_tiles);   // rows of tiles, or of tile pairs
     p.n_tiles = (N + bn - 1) / bn;
     p.k_blocks = (K + BK - 1) / BK;
 
@@ -640,7 +671,7 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles >= (1ll << 30)) return (int)cudaErrorInvalidValue;
     const int rem = (int)(tiles % st.num_sms);
-    const bool split_tail = (bn == 256) && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
+    const bool split_tail = (bn == 256) && !pair && tiles > st.num_sms && rem > 0 && 2 * rem <= st.num_sms;
     p.split_from = (int)(split_tail ? tiles - rem : tiles);
     p.num_units = (int)(split_tail ? tiles + rem : tiles);
     // Split-K: a problem with fewer tiles than half the SMs and a long K (the O and down projections of a decode
@@ -674,7 +705,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     if (p.d_tma && !make_tmap_u8_2d(&tx, D8, (uint64_t)M, (uint64_t)N, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return (int)cudaErrorInvalidValue;
 
     const int grid = (int)(p.num_units < st.num_sms ? p.num_units : st.num_sms);
-    if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
+    if (pair) fp8_gemm_tcgen05_kernel<256, 2><<<grid, NUM_THREADS, Tile<256, 2>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
+    else if (bn == 256) fp8_gemm_tcgen05_kernel<256><<<grid, NUM_THREADS, Tile<256>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
     else if (bn == 128) fp8_gemm_tcgen05_kernel<128><<<grid, NUM_THREADS, Tile<128>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
     else fp8_gemm_tcgen05_kernel<64><<<grid, NUM_THREADS, Tile<64>::SMEM_BYTES, stream>>>(ta, tb, tbh, tx, p);
     return (int)cudaGetLastError();

@@ -238,3 +238,43 @@ def test_fp8out_saturates_and_amax_optional(cuda, built_libs):
     got = got.reshape(M, N)
     assert np.all(got[:, 0::2] == 0x7E) and np.all(got[:, 1::2] == 0xFE)      # +-448, never NaN
     assert amax == 123.0                              # not asked for: not written
+
+
+def test_tile_pairs_equal_single_tiles_in_every_mode(cuda, built_libs, monkeypatch):
+    # large problems run as 256-row tile pairs (two accumulators fed from each B tile); FP8_GEMM_NO_PAIR keeps single
+    # tiles.  Same MMAs in the same order per output element -> identical bits, in all four epilogues; and sampled rows
+    # of the plain result are checked against the restatement.  M = 4224 is 33 row tiles: the last pair is half empty.
+    from goml_b200 import fp8_gemm as G
+    M, N, K, F = 4224, 19456, 2048, 9728
+    g = torch.Generator(device="cuda").manual_seed(7)
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.5).to(torch.float8_e4m3fn)
+    x0 = torch.randn(M, N, device="cuda", generator=g)
+    s = torch.tensor([0.02, 0.5, 3.0], device="cuda")
+
+    def run_all():
+        c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4, G.OutBF16, 0)
+        x = x0.clone()
+        G.FP8GEMMAccumulateF32(M, N, K, a.data_ptr(), b.data_ptr(), x.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4)
+        h = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+        am = torch.zeros(2, device="cuda")
+        G.FP8GEMMSwiGLU(M, F, K, a.data_ptr(), b.data_ptr(), h.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4, am.data_ptr())
+        d = torch.empty(M, N, dtype=torch.uint8, device="cuda")
+        G.FP8GEMMFP8Out(M, N, K, a.data_ptr(), b.data_ptr(), d.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4, s.data_ptr() + 8, am.data_ptr() + 4)
+        torch.cuda.synchronize()
+        assert G.device_status() == 0
+        return c, x, h, d, am
+
+    pair = run_all()
+    monkeypatch.setenv("FP8_GEMM_NO_PAIR", "1")
+    single = run_all()
+    for name, p_, s_ in zip(("bf16", "accumulate", "swiglu", "e4m3", "amax"), pair, single):
+        assert torch.equal(p_.view(torch.uint8) if p_.dtype != torch.uint8 else p_, s_.view(torch.uint8) if s_.dtype != torch.uint8 else s_), name
+    rows = np.array([0, 127, 128, 255, 256, 2047, 4095, 4096, 4200, 4223])
+    ah, bh = a.view(torch.uint8).cpu().numpy(), b.view(torch.uint8).cpu().numpy()
+    ref = O.gemm_f64(ah[rows], bh, float(np.float32(0.02) * np.float32(0.5)))
+    got = pair[0][torch.from_numpy(rows).cuda()].double().cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref ** 2)))
+    maxabs, meanrel = O.error_stats(got / rms, ref / rms)
+    assert maxabs <= 2e-2 and meanrel <= 1e-2, (maxabs, meanrel)
