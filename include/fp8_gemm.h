@@ -90,6 +90,9 @@ FP8GEMM_API int fp8_gemm_fp8out(int M, int N, int K, const void* A, const void* 
                                 const float* scale_a, const float* scale_b, const float* scale_d, float* amax_d,
                                 void* stream);
 
+/* Environment: FP8_GEMM_NO_PAIR (any value) makes large problems run as single 128 x 256 tiles instead of 256-row
+ * tile pairs; results are bit-identical either way (a switch for comparisons, not needed in production). */
+
 /* Additive: device-side status of the current device.  The kernels bound every
  * wait; if a wait ever runs out they record a non-zero code here and exit
  * cleanly.  This call synchronises the device and returns (and clears) the
