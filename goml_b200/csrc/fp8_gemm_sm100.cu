@@ -650,8 +650,10 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     // CTA holds two vertically adjacent 128 x 256 accumulators (both TMEM buffers) and feeds both from each B tile it
     // loads: 32 KB instead of 48 KB of operands per 128 x 256 x 128 block of MMA work (8192^3: 2739 -> 2965 TFLOP/s).
     // FP8_GEMM_NO_PAIR in the environment keeps single tiles (the parity tests compare the two, bit for bit).
+    // (One wave of pairs is enough when K is long: 4096 x 4096 x 8192 98 us against 106 us; with K = 4096 it is not.)
+    const long long pairs = ((m_tiles + 1) / 2) * ((N + 255) / 256);
     const bool pair = (bn == 256) && K >= 2048 && m_tiles >= 2 && !getenv("FP8_GEMM_NO_PAIR") &&
-                      ((m_tiles + 1) / 2) * ((N + 255) / 256) >= 2ll * st.num_sms;
+                      (pairs >= 2ll * st.num_sms || (pairs >= st.num_sms && K >= 8192));
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
