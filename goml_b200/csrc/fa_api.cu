@@ -31,7 +31,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // Checks shared by every forward entry.  `who` prefixes messages.
 fa_status_t validate(fa_ctx_t* c, const char* who, const void* q, const void* k, const void* v, const void* o,
-                     int bh, int sl, int hd, int causal, int window) {
+                     int bh, int sl, int hd, int causal, int window, const void* l_out = nullptr) {
     if (!c->arch_ok || !c->has_pool) { set_err(c, "%s: context was created on an unsupported GPU", who); return FA_ERR_UNSUPPORTED_ARCH; }
     if (!q || !k || !v || !o) { set_err(c, "%s: null pointer in q/k/v/o", who); return FA_ERR_INVALID_ARG; }
     if (bh <= 0 || sl <= 0) { set_err(c, "%s: bh/sl must be > 0", who); return FA_ERR_INVALID_ARG; }
@@ -42,6 +42,7 @@ fa_status_t validate(fa_ctx_t* c, const char* who, const void* q, const void* k,
         set_err(c, "%s: q/k/v/o must be 16-byte aligned", who);
         return FA_ERR_INVALID_ARG;
     }
+    if (reinterpret_cast<uintptr_t>(l_out) & 3) { set_err(c, "%s: l_out must be 4-byte aligned", who); return FA_ERR_INVALID_ARG; }
     if (fa_dispatch_select(bh, sl, hd, causal, window) == FA_KERNEL_NONE) {
         set_err(c, "%s: no kernel matches this configuration", who);
         return FA_ERR_UNSUPPORTED_SHAPE;
@@ -145,7 +146,7 @@ const char* fa_last_cuda_error(fa_ctx_t* ctx) { return ctx ? ctx->last_err : "";
 fa_status_t fa_forward_train(fa_ctx_t* ctx, const void* q, const void* k, const void* v, void* o, void* l_out,
                              int bh, int sl, int hd, int causal, int window, float scale, fa_stream_t stream) {
     if (!ctx) return FA_ERR_INVALID_ARG;
-    fa_status_t s = validate(ctx, "fa_forward_train", q, k, v, o, bh, sl, hd, causal, window);
+    fa_status_t s = validate(ctx, "fa_forward_train", q, k, v, o, bh, sl, hd, causal, window, l_out);
     if (s != FA_OK) return s;
     fa_sm100::LaunchArgs a{};
     a.q = q; a.k = k; a.v = v; a.o = o; a.lse = static_cast<float*>(l_out);
@@ -172,7 +173,7 @@ fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* g) {
     if (!ctx) return FA_ERR_INVALID_ARG;
     if (!g) { set_err(ctx, "%s: null argument block", "fa_forward_ex"); return FA_ERR_INVALID_ARG; }
     fa_status_t s = validate(ctx, "fa_forward_ex", g->q, g->k, g->v, g->o, g->batch_heads, g->seq_len, g->head_dim,
-                             g->causal, g->window);
+                             g->causal, g->window, g->l_out);
     if (s != FA_OK) return s;
     fa_sm100::LaunchArgs a{};
     a.q = g->q; a.k = g->k; a.v = g->v; a.o = g->o; a.lse = static_cast<float*>(g->l_out);

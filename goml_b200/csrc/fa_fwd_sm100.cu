@@ -35,6 +35,8 @@
 
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/fa_sm120.h"
 #include "fa_fwd_sm100.h"
 #include "sm100_ptx.cuh"
@@ -64,15 +66,6 @@ enum : uint32_t {
 };
 
 __device__ uint32_t g_fa_status = 0;
-
-#ifdef FA_TRACE
-// Optional in-kernel cycle trace (profiling builds only): one CTA records clock64() at the
-// phase boundaries of softmax warp 0 and of the MMA warp for its first 48 key blocks.
-__device__ long long g_fa_trace[2][48][8];
-#define TRACE(role, j, slot) do { if (trace_on && (j) < 48) g_fa_trace[role][j][slot] = clock64(); } while (0)
-#else
-#define TRACE(role, j, slot) do { } while (0)
-#endif
 
 // Shared memory holds only TMA-written operand tiles.  Both MMAs are limited by how fast the
 // tensor core can read its shared-memory operands (128 B/clk/SM), so P never goes through
@@ -180,9 +173,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef FA_TRACE
-    const bool trace_on = (blockIdx.x == 300) && (lane == 0) && (warp == 0 || warp == MMA_WARP);
-#endif
 
     // tile -> (head, query tile); within a head the tiles with the most keys come first
     const int head = blockIdx.x / p.n_qtiles;
@@ -270,11 +260,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             for (int j = 0; j < 2 && j < nblk && ok; j++) issue_qk(j);
             for (int j = 0; j < nblk && ok; j++) {
                 const int b = j & 1;
-                TRACE(1, j, 0);
                 ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, ST_TIMEOUT_MMA) &&
                      mbar_wait(bar_pfull + 8 * b, (j >> 1) & 1, abort_flag, ST_TIMEOUT_MMA);
                 if (!ok) break;
-                TRACE(1, j, 1);
                 tc_fence_after();
                 const uint32_t vaddr = sbase + C::OFF_V + vs * C::V_BYTES;
 #pragma unroll
@@ -284,13 +272,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
                 mma_commit(bar_pvdone + 8 * vs);
                 if (++vs == STAGES) { vs = 0; vph ^= 1; }
-                TRACE(1, j, 2);
                 // S[b] is rewritten by the Q K^T two blocks ahead; it is issued behind this P V on the
                 // same in-order tensor pipe, so P(j) has been read before S(j+2) lands on it
-                if (j + 2 < nblk) {
-                    issue_qk(j + 2);
-                    TRACE(1, j, 4);
-                }
+                if (j + 2 < nblk) issue_qk(j + 2);
             }
         }
     } else {
@@ -316,16 +300,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
         for (int j = 0; j < nblk; j++) {
             const int key0 = (blk0 + j) * BN;
-            TRACE(0, j, 0);
             const int b = j & 1;
             if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * rs, rph, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
-            TRACE(0, j, 1);
             tc_fence_after();
             uint32_t sreg[BN];
 #pragma unroll
             for (int c = 0; c < BN / 32; c++) tmem_ld_32x32b_x32(tmem_s + lane_off + b * BN + c * 32, sreg + c * 32);
             tmem_ld_wait();
-            TRACE(0, j, 2);
 
             if (neg) {  // out of line, on a local copy so that sreg stays in registers
                 uint32_t tmp[BN];
@@ -358,7 +339,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     mxa[t] = max3(mxa[t], __uint_as_float(sreg[c + 2 * t]), __uint_as_float(sreg[c + 2 * t + 1]));
             }
             const float mx = fmaxf(max3(max3(mxa[0], mxa[1], mxa[2]), max3(mxa[3], mxa[4], mxa[5]), mxa[6]), mxa[7]) * ascale;
-            TRACE(0, j, 3);
 
             const bool bump = mx > m_ref + TAU;  // true also on the first finite max
             const float m_new = bump ? mx : m_ref;
@@ -379,7 +359,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
             }
             m_ref = m_new;
-            TRACE(0, j, 4);
             const float nmsub = (m_ref == -INFINITY) ? 0.f : POFF - m_ref;
 
             float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
@@ -399,12 +378,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 tmem_st_32x32b_x16(tmem_s + lane_off + b * BN + g * 16, w);  // P overwrites the first half of S[b]
             }
             l += (l0 + l1) + (l2 + l3);
-            TRACE(0, j, 5);
             tmem_st_wait();
-            TRACE(0, j, 6);
             tc_fence_before();
             mbar_arrive(bar_pfull + 8 * b);
-            TRACE(0, j, 7);
             rs_prev = rs;
             rph_prev = rph;
             if (++rs == STAGES) { rs = 0; rph ^= 1; }
@@ -458,10 +434,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 }
 
 struct DeviceState {
-    bool ready = false;
+    std::once_flag once;   // first call on this device, from whichever host thread gets there first
+    cudaError_t init_error = cudaSuccess;
     int num_sms = 148;
 };
 DeviceState g_dev[64];
+
+void init_device(DeviceState* st, int dev);
 
 template <int HD>
 cudaError_t launch_hd(const LaunchArgs& a, int num_sms) {
@@ -498,6 +477,15 @@ cudaError_t launch_hd(const LaunchArgs& a, int num_sms) {
 
 }  // namespace
 
+namespace {
+void init_device(DeviceState* st, int dev) {
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&st->num_sms, cudaDevAttrMultiProcessorCount, dev);
+    st->init_error = e;
+}
+}  // namespace
+
 size_t workspace_bytes(int bh, int sl, int hd) { return (size_t)bh * sl * hd * 2; }
 
 cudaError_t launch(const LaunchArgs& a) {
@@ -506,23 +494,10 @@ cudaError_t launch(const LaunchArgs& a) {
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!a.v16_workspace || (reinterpret_cast<uintptr_t>(a.v16_workspace) & 127)) return cudaErrorInvalidValue;
-    if (!g_dev[dev].ready) {
-        e = cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        if ((e = cudaDeviceGetAttribute(&g_dev[dev].num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-        g_dev[dev].ready = true;
-    }
+    std::call_once(g_dev[dev].once, init_device, &g_dev[dev], dev);
+    if (g_dev[dev].init_error != cudaSuccess) return g_dev[dev].init_error;
     return a.hd == 128 ? launch_hd<128>(a, g_dev[dev].num_sms) : launch_hd<64>(a, g_dev[dev].num_sms);
 }
-
-#ifdef FA_TRACE
-extern "C" __attribute__((visibility("default"))) int fa_trace_read(long long* out) {
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * 2 * 48 * 8);
-}
-#endif
 
 int device_status() {
     cudaError_t e = cudaDeviceSynchronize();
@@ -557,8 +532,27 @@ static __device__ __align__(256) uint16_t g_noalloc_v16[FA_NOALLOC_MAX_ELEMS];
 namespace {
 // In host code `g_noalloc_v16` is only a stand-in for the device array; the device address is
 // looked up once per device (with that device current) and cached.
-void* g_noalloc_ptr[64];
-bool g_noalloc_ready[64];
+struct NoallocState {
+    std::once_flag once;
+    fa_status_t status = FA_OK;
+    cudaError_t cuda_error = cudaSuccess;
+    void* ptr = nullptr;
+};
+NoallocState g_noalloc[64];
+
+// One-time set-up for a device, run with that device current (do it before any stream capture): architecture
+// check and the device address of the scratch array.  With lazy module loading this is also where the driver
+// reserves the array's 32 MiB on that GPU.
+void noalloc_init(NoallocState* st, int dev) {
+    int major = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) { st->status = FA_ERR_CUDA; st->cuda_error = e; return; }
+    if (major != 10) { st->status = FA_ERR_UNSUPPORTED_ARCH; return; }
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_v16);
+    if (e != cudaSuccess || !ptr) { st->status = FA_ERR_CUDA; st->cuda_error = e; return; }
+    st->ptr = ptr;
+}
 
 void write_msg(char* err, int err_len, const char* msg) {
     if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", msg);
@@ -580,6 +574,7 @@ fa_status_t fa_forward_noalloc(const fa_forward_args_t* g, char* err, int err_le
     const uintptr_t align_or = reinterpret_cast<uintptr_t>(g->q) | reinterpret_cast<uintptr_t>(g->k) |
                                reinterpret_cast<uintptr_t>(g->v) | reinterpret_cast<uintptr_t>(g->o);
     if (align_or & 15) { write_msg(err, err_len, "fa_forward_noalloc: q/k/v/o must be 16-byte aligned"); return FA_ERR_INVALID_ARG; }
+    if (reinterpret_cast<uintptr_t>(g->l_out) & 3) { write_msg(err, err_len, "fa_forward_noalloc: l_out must be 4-byte aligned"); return FA_ERR_INVALID_ARG; }
     const size_t elems = (size_t)g->batch_heads * (size_t)g->seq_len * (size_t)g->head_dim;
     if (elems > FA_NOALLOC_MAX_ELEMS) {
         if (err && err_len > 0)
@@ -591,28 +586,24 @@ fa_status_t fa_forward_noalloc(const fa_forward_args_t* g, char* err, int err_le
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) { write_msg(err, err_len, "fa_forward_noalloc: cudaGetDevice failed"); return FA_ERR_CUDA; }
-    if (!g_noalloc_ready[dev]) {
-        // one-time set-up for this device (do it before any stream capture): architecture check and
-        // the device address of the scratch array
-        int major = 0;
-        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-        if (e != cudaSuccess) { write_msg(err, err_len, cudaGetErrorString(e)); return FA_ERR_CUDA; }
-        if (major != 10) { write_msg(err, err_len, "fa_forward_noalloc: GPU is not compute capability 10.x"); return FA_ERR_UNSUPPORTED_ARCH; }
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_noalloc_v16);
-        if (e != cudaSuccess || !ptr) {
-            if (err && err_len > 0) snprintf(err, (size_t)err_len, "fa_forward_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-            return FA_ERR_CUDA;
-        }
-        g_noalloc_ptr[dev] = ptr;
-        g_noalloc_ready[dev] = true;
+    NoallocState& st = g_noalloc[dev];
+    std::call_once(st.once, noalloc_init, &st, dev);
+    if (st.status == FA_ERR_UNSUPPORTED_ARCH) { write_msg(err, err_len, "fa_forward_noalloc: GPU is not compute capability 10.x"); return st.status; }
+    if (st.status != FA_OK) {
+        if (err && err_len > 0) snprintf(err, (size_t)err_len, "fa_forward_noalloc: set-up (cudaGetSymbolAddress): %s", cudaGetErrorString(st.cuda_error));
+        return st.status;
+    }
+    // same dispatcher consultation as the other entries, so FA_SM120_DEBUG traces every forward call alike
+    if (fa_dispatch_select(g->batch_heads, g->seq_len, g->head_dim, g->causal, g->window) == FA_KERNEL_NONE) {
+        write_msg(err, err_len, "fa_forward_noalloc: no kernel matches this configuration");
+        return FA_ERR_UNSUPPORTED_SHAPE;
     }
     LaunchArgs a{};
     a.q = g->q; a.k = g->k; a.v = g->v; a.o = g->o; a.lse = static_cast<float*>(g->l_out);
     a.bh = g->batch_heads; a.sl = g->seq_len; a.hd = g->head_dim; a.causal = g->causal; a.window = g->window;
     a.scale = g->scale; a.v_descale = (g->v_descale == 0.0f) ? 1.0f : g->v_descale;
     a.scale_q_dev = g->scale_q_dev; a.scale_k_dev = g->scale_k_dev; a.scale_v_dev = g->scale_v_dev;
-    a.v16_workspace = g_noalloc_ptr[dev];
+    a.v16_workspace = st.ptr;
     a.stream = reinterpret_cast<cudaStream_t>(g->stream);
     e = launch(a);
     if (e != cudaSuccess) {
@@ -621,3 +612,8 @@ fa_status_t fa_forward_noalloc(const fa_forward_args_t* g, char* err, int err_le
     }
     return FA_OK;
 }
+
+// Context-free twin of fa_device_status for callers of fa_forward_noalloc, which have no fa_ctx_t (creating one
+// would create a memory pool, the very thing they avoid).  Synchronises the current device; allocates nothing.
+extern "C" __attribute__((visibility("default")))
+int fa_noalloc_device_status(void) { return fa_sm100::device_status(); }

@@ -20,6 +20,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "../../include/fp8_gemm.h"
 #include "sm100_ptx.cuh"
 #include "tmap.cuh"
@@ -64,10 +67,6 @@ enum : uint32_t {
 };
 
 __device__ uint32_t g_gemm_status = 0;  // first non-zero code any CTA reported (per device)
-
-#ifndef FP8_GEMM_C_TMA
-#define FP8_GEMM_C_TMA 1
-#endif
 
 struct GemmParams {
     int M, N, K;
@@ -415,7 +414,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     }
                     sbuf ^= 1;
                 }
-            } else if (FP8_GEMM_C_TMA && p.c_tma) {
+            } else if (p.c_tma) {
                 // 16-bit C through the memory system: two 32-column chunks of this warp's 32 rows fill one 32 x 64 box
                 // (128-byte rows, swizzled like the fp32 boxes of the accumulate mode), one TMA store per box,
                 // double-buffered; rows >= M and columns >= N are clipped by the tensor map
@@ -565,7 +564,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
         }
     epilogue_done:
-        if (((p.X && p.x_tma) || (FP8_GEMM_C_TMA && p.c_tma) || p.h_tma || p.d_tma) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
+        if (((p.X && p.x_tma) || p.c_tma || p.h_tma || p.d_tma) && lane == 0) tma_store_wait<0>();  // every reduce has left shared memory and been performed
     }
 
     // ------------------------------------------------------------- teardown
@@ -591,11 +590,42 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 constexpr int Tile_KSUB(int bn) { return bn == 256 ? Tile<256>::KSUB : bn == 128 ? Tile<128>::KSUB : Tile<64>::KSUB; }
 
 struct DeviceState {
-    bool ready = false;
+    std::once_flag once;      // first call on this device, from whichever host thread gets there first
+    cudaError_t init_error = cudaSuccess;
     int num_sms = 0;
 };
 constexpr int MAX_DEVICES = 64;
 DeviceState g_dev[MAX_DEVICES];
+
+// Tile-pair policy: -1 = choose per problem (default), 0 = never (single tiles only).  The environment variable
+// FP8_GEMM_NO_PAIR is read once, at the first launch of the process; fp8_gemm_set_tile_pairs overrides it.
+std::atomic<int> g_pair_policy{-2};  // -2 = environment not read yet
+int pair_policy() {
+    int v = g_pair_policy.load(std::memory_order_acquire);
+    if (v == -2) {
+        int from_env = getenv("FP8_GEMM_NO_PAIR") ? 0 : -1;
+        g_pair_policy.compare_exchange_strong(v, from_env, std::memory_order_acq_rel);
+        v = g_pair_policy.load(std::memory_order_acquire);
+    }
+    return v;
+}
+
+void init_device(DeviceState* st, int dev) {
+    int major = 0, sms = 0;
+    cudaError_t e;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) { st->init_error = e; return; }
+    if (major != 10) { st->init_error = cudaErrorNoKernelImageForDevice; return; }
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) { st->init_error = e; return; }
+    if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Tile<256>::SMEM_BYTES)) != cudaSuccess) { st->init_error = e; return; }
+    if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Tile<256, 2>::SMEM_BYTES)) != cudaSuccess) { st->init_error = e; return; }
+    if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Tile<128>::SMEM_BYTES)) != cudaSuccess) { st->init_error = e; return; }
+    if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Tile<64>::SMEM_BYTES)) != cudaSuccess) { st->init_error = e; return; }
+    st->num_sms = sms;
+}
 
 int launch(int M, int N, int K, const void* A, const void* B, void* C, float alpha, const float* sa, const float* sb,
            int out_bf16, cudaStream_t stream, float* X = nullptr, void* H = nullptr, int F = 0, float* amax = nullptr,
@@ -614,22 +644,8 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= MAX_DEVICES) return (int)cudaErrorInvalidDevice;
     DeviceState& st = g_dev[dev];
-    if (!st.ready) {
-        int major = 0, sms = 0;
-        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return (int)e;
-        if (major != 10) return (int)cudaErrorNoKernelImageForDevice;
-        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Tile<256>::SMEM_BYTES)) != cudaSuccess) return (int)e;
-        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Tile<256, 2>::SMEM_BYTES)) != cudaSuccess) return (int)e;
-        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Tile<128>::SMEM_BYTES)) != cudaSuccess) return (int)e;
-        if ((e = cudaFuncSetAttribute(fp8_gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Tile<64>::SMEM_BYTES)) != cudaSuccess) return (int)e;
-        st.num_sms = sms;
-        st.ready = true;
-    }
+    std::call_once(st.once, init_device, &st, dev);
+    if (st.init_error != cudaSuccess) return (int)st.init_error;
 
     // Tile width: 256 unless a narrower tile cuts (waves x per-k-block MMA time) by more than a quarter —
     // i.e. only when the 128x256 tiling leaves most SMs idle (small or skinny problems).  Per-k-block MMA
@@ -649,11 +665,23 @@ int launch(int M, int N, int K, const void* A, const void* B, void* C, float alp
     // Tile pairs: with at least two waves of 256 x 256 pairs and a K long enough to amortise the three-stage ring, a
     // CTA holds two vertically adjacent 128 x 256 accumulators (both TMEM buffers) and feeds both from each B tile it
     // loads: 32 KB instead of 48 KB of operands per 128 x 256 x 128 block of MMA work (8192^3: 2739 -> 2965 TFLOP/s).
-    // FP8_GEMM_NO_PAIR in the environment keeps single tiles (the parity tests compare the two, bit for bit).
     // (One wave of pairs is enough when K is long: 4096 x 4096 x 8192 98 us against 106 us; with K = 4096 it is not.)
+    // A pair-wave costs two tile-waves at about 0.92 of their time, and pair mode has no half-width last wave, so
+    // pairs are taken only when that estimate does not lose to single tiles: a pair count just above a multiple of
+    // the SM count (150 pairs on 148 SMs) would pay a whole extra double-cost wave.
+    // fp8_gemm_set_tile_pairs(0) or FP8_GEMM_NO_PAIR in the environment keeps single tiles (the parity tests compare
+    // the two, bit for bit).
     const long long pairs = ((m_tiles + 1) / 2) * ((N + 255) / 256);
-    const bool pair = (bn == 256) && K >= 2048 && m_tiles >= 2 && !getenv("FP8_GEMM_NO_PAIR") &&
-                      (pairs >= 2ll * st.num_sms || (pairs >= st.num_sms && K >= 8192));
+    bool pair = (bn == 256) && K >= 2048 && m_tiles >= 2 && pair_policy() != 0 &&
+                (pairs >= 2ll * st.num_sms || (pairs >= st.num_sms && K >= 8192));
+    if (pair) {
+        const long long tiles1 = m_tiles * ((N + 255) / 256);
+        const long long rem1 = tiles1 % st.num_sms;
+        // single tiles, in hundredths of a wave; a half-width last wave was measured at about 0.9 of a full one
+        const long long single_cost = (tiles1 / st.num_sms) * 100 + (rem1 == 0 ? 0 : (2 * rem1 <= st.num_sms ? 90 : 100));
+        const long long pair_cost = ((pairs + st.num_sms - 1) / st.num_sms) * 2 * 92;
+        if (pair_cost > single_cost) pair = false;
+    }
     GemmParams p;
     p.M = M; p.N = N; p.K = K; p.C = C;
     p.alpha = alpha; p.scale_a = sa; p.scale_b = sb; p.out_bf16 = out_bf16;
@@ -771,6 +799,12 @@ int fp8_gemm_device_status(void) {
     if (e != cudaSuccess) return -(int)e;
     if (code != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero));
     return (int)code;
+}
+
+int fp8_gemm_set_tile_pairs(int mode) {
+    if (mode != 0 && mode != -1) return (int)cudaErrorInvalidValue;
+    g_pair_policy.store(mode, std::memory_order_release);
+    return 0;
 }
 
 const char* fp8_gemm_version(void) { return "1.0.0+tcgen05-sm100a"; }

@@ -49,6 +49,8 @@ def _init():
                 lib.fp8_gemm_fp8out.restype = i
                 lib.fp8_gemm_fp8out.argtypes = [i, i, i, p, p, p, f, p, p, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
+                lib.fp8_gemm_set_tile_pairs.restype = i
+                lib.fp8_gemm_set_tile_pairs.argtypes = [i]
                 lib.fp8_gemm_version.restype = C.c_char_p
                 _state["lib"] = lib
             except OSError as e:
@@ -126,6 +128,13 @@ def interleave_gate_up(w_gate_up, F: int):
         out[full, 0, :F % 32] = gate[32 * full:]
         out[full, 1, :F % 32] = up[32 * full:]
     return out.reshape(2 * Fp, K)
+
+
+def SetTilePairs(mode: int) -> None:
+    """-1 = tile pairs chosen per problem (default), 0 = single tiles only; results are bit-identical."""
+    rc = _init().fp8_gemm_set_tile_pairs(mode)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_set_tile_pairs: CUDA error {rc}")
 
 
 def device_status() -> int:

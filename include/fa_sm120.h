@@ -160,8 +160,17 @@ FA_API fa_status_t fa_forward_ex(fa_ctx_t* ctx, const fa_forward_args_t* args);
  * context is needed.  err/err_len: optional caller buffer that receives a message on failure.
  * The array is shared by all calls on a GPU: calls whose GPU work overlaps race on it — use
  * one stream or serialise.  The first call on each device performs a one-time set-up
- * (device address of the array, kernel attributes); make it before any stream capture. */
+ * (device address of the array, kernel attributes); make it before any stream capture.
+ * Where the CUDA runtime loads modules lazily, that first call is also the moment the driver
+ * reserves the 32 MiB on that GPU: a process that freezes its memory map must make the first
+ * call (a one-row problem will do) during start-up, not merely before capture. */
 FA_API fa_status_t fa_forward_noalloc(const fa_forward_args_t* args, char* err, int err_len);
+
+/* No counterpart in the reference: fa_device_status for callers without a context (users of
+ * fa_forward_noalloc; fa_create would create a memory pool).  Synchronises the current device
+ * and returns, and clears, the first bounded-wait expiry code an attention kernel recorded:
+ * 0 = none, > 0 = the code, < 0 = a CUDA error code negated.  Allocates nothing. */
+FA_API int fa_noalloc_device_status(void);
 
 /* No counterpart in the reference (designed on paper there, runs/reports/F1_HF_INFERENCE_recon.md:55-68,163): the
  * decode step of quantised inference — one new token per sequence attends to an FP8 KV cache, with grouped-query

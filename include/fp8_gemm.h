@@ -90,8 +90,12 @@ FP8GEMM_API int fp8_gemm_fp8out(int M, int N, int K, const void* A, const void* 
                                 const float* scale_a, const float* scale_b, const float* scale_d, float* amax_d,
                                 void* stream);
 
-/* Environment: FP8_GEMM_NO_PAIR (any value) makes large problems run as single 128 x 256 tiles instead of 256-row
- * tile pairs; results are bit-identical either way (a switch for comparisons, not needed in production). */
+/* Additive: tile-pair policy of this process.  mode -1 = chosen per problem (default), 0 = large problems run as
+ * single 128 x 256 tiles instead of 256-row tile pairs; other values return cudaErrorInvalidValue.  Results are
+ * bit-identical either way (a switch for comparisons, not needed in production).  The environment variable
+ * FP8_GEMM_NO_PAIR (any value) selects mode 0; it is read once, at the first launch of the process, and a call of
+ * this function overrides it. */
+FP8GEMM_API int fp8_gemm_set_tile_pairs(int mode);
 
 /* Additive: device-side status of the current device.  The kernels bound every
  * wait; if a wait ever runs out they record a non-zero code here and exit

@@ -240,8 +240,8 @@ def test_fp8out_saturates_and_amax_optional(cuda, built_libs):
     assert amax == 123.0                              # not asked for: not written
 
 
-def test_tile_pairs_equal_single_tiles_in_every_mode(cuda, built_libs, monkeypatch):
-    # large problems run as 256-row tile pairs (two accumulators fed from each B tile); FP8_GEMM_NO_PAIR keeps single
+def test_tile_pairs_equal_single_tiles_in_every_mode(cuda, built_libs):
+    # large problems run as 256-row tile pairs (two accumulators fed from each B tile); fp8_gemm_set_tile_pairs(0) keeps single
     # tiles.  Same MMAs in the same order per output element -> identical bits, in all four epilogues; and sampled rows
     # of the plain result are checked against the restatement.  M = 4224 is 33 row tiles: the last pair is half empty.
     from goml_b200 import fp8_gemm as G
@@ -267,8 +267,11 @@ def test_tile_pairs_equal_single_tiles_in_every_mode(cuda, built_libs, monkeypat
         return c, x, h, d, am
 
     pair = run_all()
-    monkeypatch.setenv("FP8_GEMM_NO_PAIR", "1")
-    single = run_all()
+    G.SetTilePairs(0)
+    try:
+        single = run_all()
+    finally:
+        G.SetTilePairs(-1)
     for name, p_, s_ in zip(("bf16", "accumulate", "swiglu", "e4m3", "amax"), pair, single):
         assert torch.equal(p_.view(torch.uint8) if p_.dtype != torch.uint8 else p_, s_.view(torch.uint8) if s_.dtype != torch.uint8 else s_), name
     rows = np.array([0, 127, 128, 255, 256, 2047, 4095, 4096, 4200, 4223])
