@@ -82,6 +82,80 @@ __global__ void __launch_bounds__(THREADS) dequant_kernel(const uint8_t* __restr
     }
 }
 
+// ---- FP16 sources: the reference's own entry point (libs1/fp8_quantize_v2.cu:176-204) has no stream, no amax
+// argument and allocates its reduction buffer itself; here the amax word is a per-GPU device variable, so the
+// entry allocates nothing.  Calls run on the legacy default stream like the reference's and therefore serialise.
+__device__ float g_amax_fp16;
+
+__global__ void clear_amax_fp16_kernel() { g_amax_fp16 = 0.f; }
+
+__global__ void __launch_bounds__(THREADS) amax_fp16_kernel(const __half* __restrict__ x, int n) {
+    // 8 halves (16 bytes) per step when the pointer allows it, else element by element
+    float m = 0.f;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const size_t n8 = (size_t)n / 8;
+        const uint4* x8 = reinterpret_cast<const uint4*>(x);
+        for (size_t i = tid; i < n8; i += stride) {
+            const uint4 v = __ldg(x8 + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
+        }
+        for (size_t i = n8 * 8 + tid; i < (size_t)n; i += stride) m = fmaxf(m, fabsf(__half2float(x[i])));
+    } else {
+        for (size_t i = tid; i < (size_t)n; i += stride) m = fmaxf(m, fabsf(__half2float(x[i])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float wm[THREADS / 32];
+    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < THREADS / 32 ? wm[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(&g_amax_fp16), __float_as_uint(m));
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) quant_fp16_kernel(const __half* __restrict__ x, uint8_t* __restrict__ q, int n,
+                                                             float* scale_out) {
+    // operation order of libs1/fp8_quantize_v2.cu:89-121: scale = amax / 448, inv = 1 / scale, v = float(x) * inv,
+    // clamp to +-448, round to nearest even
+    const float amax = g_amax_fp16;
+    const float scale = (amax > 1e-12f) ? __fdiv_rn(amax, 448.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(q) & 7) == 0);
+    const size_t n8 = vec ? (size_t)n / 8 : 0;
+    const uint4* x8 = reinterpret_cast<const uint4*>(x);
+    uint2* q8 = reinterpret_cast<uint2*>(q);
+    for (size_t i = tid; i < n8; i += stride) {
+        const uint4 v = __ldg(x8 + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t c[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            const float a = fminf(fmaxf(__fmul_rn(f.x, inv), -448.f), 448.f);
+            const float b = fminf(fmaxf(__fmul_rn(f.y, inv), -448.f), 448.f);
+            c[k] = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        }
+        q8[i] = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+    }
+    for (size_t i = n8 * 8 + tid; i < (size_t)n; i += stride) {
+        const float v = fminf(fmaxf(__fmul_rn(__half2float(x[i]), inv), -448.f), 448.f);
+        q[i] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+    }
+}
+
 int grid_for(size_t work_items) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -116,5 +190,16 @@ int fp8_dequantize_to_fp16(const void* input_fp8, void* output_fp16, const float
     dequant_kernel<<<grid_for((size_t)n), THREADS>>>((const uint8_t*)input_fp8, (__half*)output_fp16, scale_in, n);
     return (int)cudaGetLastError();
 }
+
+int fp8_quantize_fp16(const void* input_fp16, void* output_fp8, float* scale_out, int n) {
+    if (!input_fp16 || !output_fp8 || !scale_out || n < 0) return (int)cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(input_fp16) & 1) return (int)cudaErrorInvalidValue;
+    clear_amax_fp16_kernel<<<1, 1>>>();
+    if (n > 0) amax_fp16_kernel<<<grid_for((size_t)n / 8 + 1), THREADS>>>((const __half*)input_fp16, n);
+    quant_fp16_kernel<<<grid_for((size_t)n / 8 + 1), THREADS>>>((const __half*)input_fp16, (uint8_t*)output_fp8, n, scale_out);
+    return (int)cudaGetLastError();
+}
+
+int cuda_device_sync2(void) { return (int)cudaDeviceSynchronize(); }
 
 }  // extern "C"

@@ -34,6 +34,9 @@ def _init():
             lib.fp8_quantize_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
             lib.fp8_dequantize_to_fp16.restype = C.c_int
             lib.fp8_dequantize_to_fp16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+            lib.fp8_quantize_fp16.restype = C.c_int
+            lib.fp8_quantize_fp16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+            lib.cuda_device_sync2.restype = C.c_int
             _lib = lib
     return _lib
 
@@ -54,3 +57,16 @@ def DequantizeToFP16(src: int, dst: int, scale: int, n: int) -> None:
     rc = _init().fp8_dequantize_to_fp16(src, dst, scale, n)
     if rc != 0:
         raise QuantizeError(f"fp8_dequantize_to_fp16: CUDA error {rc}")
+
+
+def QuantizeFP16(src: int, dst: int, scale: int, n: int) -> None:
+    """fp8_quantize_fp16 of libs1/fp8_quantize_v2.cu:176-204: FP16 source, scale = amax/448, default stream."""
+    rc = _init().fp8_quantize_fp16(src, dst, scale, n)
+    if rc != 0:
+        raise QuantizeError(f"fp8_quantize_fp16: CUDA error {rc}")
+
+
+def DeviceSync2() -> None:
+    rc = _init().cuda_device_sync2()
+    if rc != 0:
+        raise QuantizeError(f"cuda_device_sync2: CUDA error {rc}")

@@ -50,6 +50,17 @@ FP8QUANT_API int fp8_quantize_f32(const float* x, uint8_t* q, float* scale_out, 
  * fp16(decode(q[i]) * *scale_in). */
 FP8QUANT_API int fp8_dequantize_to_fp16(const void* input_fp8, void* output_fp16, const float* scale_in, int n);
 
+/* Replaces fp8_quantize_fp16 (libs1/fp8_quantize_v2.cu:176-204), same signature: n FP16 values -> n e4m3 codes with
+ * scale = amax / 448 written to *scale_out; runs on the legacy default stream and returns without synchronising,
+ * as the reference does.  Differences: argument errors return cudaErrorInvalidValue instead of faulting, and
+ * nothing is allocated (the reference grows a cudaMalloc'ed reduction buffer; here the amax is one device word
+ * inside the library, shared by all calls on a GPU, which the default stream serialises).  Codes and scale are
+ * bit-identical to the reference's. */
+FP8QUANT_API int fp8_quantize_fp16(const void* input_fp16, void* output_fp8, float* scale_out, int n);
+
+/* Replaces cuda_device_sync2 (libs1/fp8_quantize_v2.cu:216): cudaDeviceSynchronize() as int. */
+FP8QUANT_API int cuda_device_sync2(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,10 +24,26 @@ _f32p = C.POINTER(C.c_float)
 _f64p = C.POINTER(C.c_double)
 
 
+def reference_root() -> str:
+    """Where the reference tree lies, or "" when it is not on this machine: $GOML_REFERENCE, else the
+    ``reference_path`` entry of BASELINE.json at the repository root."""
+    cand = os.environ.get("GOML_REFERENCE", "")
+    if not cand:
+        try:
+            import json
+            with open(os.path.join(os.path.dirname(_HERE), "BASELINE.json")) as f:
+                cand = json.load(f).get("reference_path", "")
+        except (OSError, ValueError):
+            cand = ""
+    return cand if cand and os.path.isdir(os.path.join(cand, "libs")) else ""
+
+
 def build(ref: bool = True) -> None:
     """Compile liboracle.so (and oracle/_ref when the reference tree is there)."""
-    target = "all" if ref else os.path.join(_HERE, "liboracle.so")
-    subprocess.run(["make", "-C", _HERE, target], check=True, capture_output=True)
+    root = reference_root() if ref else ""
+    target = "all" if root else os.path.join(_HERE, "liboracle.so")
+    cmd = ["make", "-C", _HERE, target] + ([f"REF={root}"] if root else [])
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 _lib = None
@@ -228,6 +244,13 @@ class Ref:
         self.fa128 = self._open(os.path.join(d, "libref_fa_hd128.so"))
         self.fa64 = self._open(os.path.join(d, "libref_fa_hd64.so"))
         self.gemm = self._open(os.path.join(d, "libref_gemm.so"))
+        # the reference's quantiser kernels (libs1/fp8_quantize_v2.cu:159-217), compiled for this GPU as they stand:
+        # GPU code, used by the -m gpu tests to pin e4m3 codes to the reference's own output
+        self.quant = self._open(os.path.join(d, "libref_quant.so"))
+        if self.quant is not None:
+            self.quant.fp8_quantize_fp16.restype = C.c_int
+            self.quant.fp8_quantize_fp16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+            self.quant.cuda_device_sync2.restype = C.c_int
         for L in (self.fa128, self.fa64):
             if L is not None:
                 L.ref_cpu_attention_fp8.argtypes = [_u8p, _u8p, _u8p, _f32p] + [C.c_int] * 5

@@ -12,6 +12,9 @@
 #undef main
 
 extern "C" {
+/* the harness program itself (self-check, bench table, --time/--ncu/--loop modes: same file :757-1130) */
+__attribute__((visibility("default")))
+int ref_fa_harness(int argc, char **argv) { return ref_harness_main(argc, argv); }
 /* cpu_attention_fp8: .../flash_attention_v121r_diet_hd128_fp8_forward.cu:709-752 */
 __attribute__((visibility("default")))
 void ref_cpu_attention_fp8(const uint8_t *Q, const uint8_t *K, const uint8_t *V, float *O,

@@ -74,7 +74,8 @@ def test_dispatch_table(built_libs):
 
 
 def test_reference_dispatch_test_program_passes_unchanged(built_libs, tmp_path):
-    src = "/root/reference/libs/fa_sm120/test/test_dispatch.c"
+    import oracle
+    src = os.path.join(oracle.reference_root(), "libs/fa_sm120/test/test_dispatch.c")
     if not os.path.exists(src) or not shutil.which("gcc"):
         pytest.skip("reference tree not present")
     exe = tmp_path / "test_dispatch"
