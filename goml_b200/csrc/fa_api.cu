@@ -235,6 +235,14 @@ fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* g) {
     return FA_OK;
 }
 
+fa_status_t fa_selftest_wait_expiry(fa_ctx_t* ctx, fa_stream_t stream) {
+    if (!ctx) return FA_ERR_INVALID_ARG;
+    if (!ctx->arch_ok) { set_err(ctx, "%s: context was created on an unsupported GPU", "fa_selftest_wait_expiry"); return FA_ERR_UNSUPPORTED_ARCH; }
+    const cudaError_t e = fa_sm100::launch_wait_expiry_selftest(reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { set_err(ctx, "%s: launch: %s", "fa_selftest_wait_expiry", cudaGetErrorString(e)); return FA_ERR_CUDA; }
+    return FA_OK;
+}
+
 fa_status_t fa_device_status(fa_ctx_t* ctx) {
     if (!ctx) return FA_ERR_INVALID_ARG;
     const int code = fa_sm100::device_status();

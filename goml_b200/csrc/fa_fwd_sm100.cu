@@ -63,6 +63,7 @@ enum : uint32_t {
     ST_TIMEOUT_MMA = 0x202,
     ST_TIMEOUT_SOFTMAX = 0x203,
     ST_BAD_SMEM_ALIGN = 0x204,
+    ST_TIMEOUT_SELFTEST = 0x2F0,   // fa_selftest_wait_expiry
 };
 
 __device__ uint32_t g_fa_status = 0;
@@ -127,6 +128,10 @@ __device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(32) fa_wait_expiry_selftest_kernel() {
+    wait_expiry_selftest_body(&g_fa_status, ST_TIMEOUT_SELFTEST);
 }
 
 // V (e4m3) -> fp16, 16 codes per thread per step; exact.
@@ -497,6 +502,11 @@ cudaError_t launch(const LaunchArgs& a) {
     std::call_once(g_dev[dev].once, init_device, &g_dev[dev], dev);
     if (g_dev[dev].init_error != cudaSuccess) return g_dev[dev].init_error;
     return a.hd == 128 ? launch_hd<128>(a, g_dev[dev].num_sms) : launch_hd<64>(a, g_dev[dev].num_sms);
+}
+
+cudaError_t launch_wait_expiry_selftest(cudaStream_t stream) {
+    fa_wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>();
+    return cudaGetLastError();
 }
 
 int device_status() {

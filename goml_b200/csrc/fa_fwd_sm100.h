@@ -55,6 +55,9 @@ inline int decode_span(const DecodeArgs& a) { return a.seq_lens ? a.s_max : a.se
 size_t decode_workspace_bytes(int batch, int kv_heads, int head_dim, int span);
 cudaError_t launch_decode(const DecodeArgs& a);
 
+// One warp that lets a 1 ms bounded wait run out on a barrier nothing arrives at and latches code 0x2F0.
+cudaError_t launch_wait_expiry_selftest(cudaStream_t stream);
+
 // Synchronises the device and returns (and clears) the first non-zero status
 // code a kernel recorded (a wait that ran out), 0 if none, -cudaError on failure.
 int device_status();

@@ -64,6 +64,7 @@ enum : uint32_t {
     ST_TIMEOUT_PRODUCER = 0x101,
     ST_TIMEOUT_MMA = 0x102,
     ST_TIMEOUT_EPILOGUE = 0x103,
+    ST_TIMEOUT_SELFTEST = 0x1F0,   // fp8_gemm_selftest_wait_expiry
 };
 
 __device__ uint32_t g_gemm_status = 0;  // first non-zero code any CTA reported (per device)
@@ -585,6 +586,10 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
 }
 
+__global__ void __launch_bounds__(32) gemm_wait_expiry_selftest_kernel() {
+    wait_expiry_selftest_body(&g_gemm_status, ST_TIMEOUT_SELFTEST);
+}
+
 // ---------------------------------------------------------------- host side
 
 constexpr int Tile_KSUB(int bn) { return bn == 256 ? Tile<256>::KSUB : bn == 128 ? Tile<128>::KSUB : Tile<64>::KSUB; }
@@ -799,6 +804,11 @@ int fp8_gemm_device_status(void) {
     if (e != cudaSuccess) return -(int)e;
     if (code != 0) cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(zero));
     return (int)code;
+}
+
+int fp8_gemm_selftest_wait_expiry(void* stream) {
+    gemm_wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>();
+    return (int)cudaGetLastError();
 }
 
 int fp8_gemm_set_tile_pairs(int mode) {

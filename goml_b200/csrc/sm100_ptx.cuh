@@ -67,7 +67,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 #endif
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t code) {
+                                          uint32_t code, uint64_t budget_ns = SM100_WAIT_BUDGET_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     uint32_t polls = 0;
@@ -78,11 +78,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > SM100_WAIT_BUDGET_NS) {
+            else if (now - t0 > budget_ns) {
                 atomicCAS((uint32_t*)abort_flag, 0u, code);
                 return false;
             }
         }
+    }
+}
+
+// Self-test of the bounded wait, shared by the libraries: one warp waits, with a 1 ms budget, on a barrier that
+// nothing will ever arrive at.  The wait must give up, set the CTA's abort word to `code`, and the kernel then latches
+// the code into the library's device status word exactly as a production kernel's teardown does — and returns.
+// No TMA, no tensor memory, nothing in flight: the only thing exercised is the expiry path itself.
+__device__ __forceinline__ void wait_expiry_selftest_body(uint32_t* device_status_word, uint32_t code) {
+    __shared__ __align__(8) uint64_t bar_storage;
+    __shared__ uint32_t abort_word;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        abort_word = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const bool completed = mbar_wait(bar, 0, &abort_word, code, 1000000ull /* 1 ms */);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // completed == true would mean the wait returned without anybody arriving: report that as its own code
+        const uint32_t latched = completed ? (code | 0x8000u) : abort_word;
+        if (latched != 0) atomicCAS(device_status_word, 0u, latched);
     }
 }
 

@@ -124,6 +124,10 @@ def FALoad():
                 lib.fa_decode.argtypes = [p, C.POINTER(DecodeArgs)]
                 lib.fa_device_status.restype = i
                 lib.fa_device_status.argtypes = [p]
+                lib.fa_noalloc_device_status.restype = i
+                lib.fa_noalloc_device_status.argtypes = []
+                lib.fa_selftest_wait_expiry.restype = i
+                lib.fa_selftest_wait_expiry.argtypes = [p, p]
                 _lib = lib
                 break
             if _lib is None:
@@ -213,6 +217,12 @@ class FAContext:
         if st != FA_OK:
             raise FAError("fa_device_status", st, self._msg())
 
+    def SelftestWaitExpiry(self, stream=0) -> None:
+        """Launch the one-warp kernel whose bounded wait runs out; the next DeviceStatus() then raises FA_ERR_INTERNAL."""
+        st = FALoad().fa_selftest_wait_expiry(self.ptr, stream or None)
+        if st != FA_OK:
+            raise FAError("fa_selftest_wait_expiry", st, self._msg())
+
     def __enter__(self):
         return self
 
@@ -235,6 +245,12 @@ def FAForwardNoAlloc(q, k, v, o, lOut, bh, sl, hd, causal, window, scale, v_desc
     st = FALoad().fa_forward_noalloc(C.byref(a), buf, len(buf))
     if st != FA_OK:
         raise FAError("fa_forward_noalloc", st, buf.value.decode(errors="replace"))
+
+
+def FANoAllocDeviceStatus() -> int:
+    """fa_device_status without a context (for users of FAForwardNoAlloc): 0, a kernel's wait-expiry code, or
+    a negated CUDA error."""
+    return FALoad().fa_noalloc_device_status()
 
 
 def FACreate() -> FAContext:

@@ -49,6 +49,8 @@ def _init():
                 lib.fp8_gemm_fp8out.restype = i
                 lib.fp8_gemm_fp8out.argtypes = [i, i, i, p, p, p, f, p, p, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
+                lib.fp8_gemm_selftest_wait_expiry.restype = i
+                lib.fp8_gemm_selftest_wait_expiry.argtypes = [p]
                 lib.fp8_gemm_set_tile_pairs.restype = i
                 lib.fp8_gemm_set_tile_pairs.argtypes = [i]
                 lib.fp8_gemm_version.restype = C.c_char_p
@@ -135,6 +137,13 @@ def SetTilePairs(mode: int) -> None:
     rc = _init().fp8_gemm_set_tile_pairs(mode)
     if rc != 0:
         raise FP8GEMMError(f"fp8_gemm_set_tile_pairs: CUDA error {rc}")
+
+
+def SelftestWaitExpiry(stream: int = 0) -> None:
+    """Launch the one-warp kernel whose bounded wait runs out; the next device_status() then returns 0x1F0."""
+    rc = _init().fp8_gemm_selftest_wait_expiry(stream or None)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_selftest_wait_expiry: CUDA error {rc}")
 
 
 def device_status() -> int:

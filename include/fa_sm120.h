@@ -216,6 +216,13 @@ FA_API fa_status_t fa_decode(fa_ctx_t* ctx, const fa_decode_args_t* args);
  * with the code in fa_last_cuda_error. */
 FA_API fa_status_t fa_device_status(fa_ctx_t* ctx);
 
+/* No counterpart in the reference: self-test of the bounded waits.  Launches one warp that waits, with a 1 ms budget,
+ * on a barrier nothing ever arrives at; the wait gives up and the kernel returns after latching code 0x2F0 the way an
+ * attention kernel's teardown would.  The next fa_device_status() must therefore return FA_ERR_INTERNAL with
+ * "device status 0x2f0" as the message, and the one after that FA_OK.  No operand memory, TMA or tensor memory is
+ * touched; the GPU context stays usable. */
+FA_API fa_status_t fa_selftest_wait_expiry(fa_ctx_t* ctx, fa_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

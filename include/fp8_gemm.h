@@ -103,6 +103,12 @@ FP8GEMM_API int fp8_gemm_set_tile_pairs(int mode);
  * code; 0 = no kernel reported a problem.  Negative = CUDA error code negated. */
 FP8GEMM_API int fp8_gemm_device_status(void);
 
+/* Additive: self-test of the bounded waits.  Launches one warp that waits, with a 1 ms budget, on a barrier nothing
+ * ever arrives at; the wait gives up and the kernel returns after latching code 0x1F0 the way a production kernel's
+ * teardown would.  The next fp8_gemm_device_status() must therefore return 0x1F0, and the one after that 0.  Touches
+ * no operand memory, no TMA, no tensor memory; the GPU context stays usable. */
+FP8GEMM_API int fp8_gemm_selftest_wait_expiry(void* stream);
+
 /* Additive: static version string. */
 FP8GEMM_API const char* fp8_gemm_version(void);
 

@@ -220,3 +220,45 @@ def test_config3_full_size_sampled(fa_ctx, causal):
                      1.0 / math.sqrt(hd), 1.0, scales.data_ptr(), scales.data_ptr() + 8, scales.data_ptr() + 16)
     torch.cuda.synchronize()
     assert torch.equal(o2[9], o2[5]) and torch.equal(o2[5], o[5])
+
+
+# the long-sequence cells of the sweep (B*S = 65536 tokens, H = 32): 64-bit indexing, grids of 16384 CTAs
+@pytest.mark.parametrize("causal", [0, 1])
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("bh,sl", [(128, 16384), (64, 32768), (512, 4096), (2048, 1024)])
+def test_sweep_cells_on_sampled_blocks(fa_ctx, bh, sl, hd, causal):
+    # inputs drawn on the device from a fixed Philox seed and quantised there; the same code bytes and scales are copied
+    # back for the oracle, which is evaluated on three (head, 32-row) blocks
+    from goml_b200 import quantize as Q
+    g = torch.Generator(device="cuda").manual_seed(bh * 7 + sl + hd)
+    codes, scales = [], torch.zeros(6, dtype=torch.float32, device="cuda")
+    for i in range(3):
+        t = torch.randn((bh, sl, hd), generator=g, device="cuda")
+        c = torch.empty((bh, sl, hd), dtype=torch.uint8, device="cuda")
+        Q.QuantizeF32ToF8E4M3(t.data_ptr(), c.data_ptr(), scales.data_ptr() + 8 * i, scales.data_ptr() + 8 * i + 4, t.numel(), 0)
+        torch.cuda.synchronize()
+        del t
+        codes.append(c)
+    q, k, v = codes
+    o = torch.zeros((bh, sl, hd), dtype=torch.float16, device="cuda")
+    lse = torch.zeros((bh, sl), dtype=torch.float32, device="cuda")
+    fa_ctx.ForwardEx(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), bh, sl, hd, causal, 0,
+                     1.0 / math.sqrt(hd), 1.0, scales.data_ptr(), scales.data_ptr() + 8, scales.data_ptr() + 16)
+    torch.cuda.synchronize()
+    fa_ctx.DeviceStatus()
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    sc = scales.cpu().numpy()
+    scale = float(sc[0]) * float(sc[2]) / math.sqrt(hd)
+    for h, r0 in [(0, 0), (bh // 3, sl // 2 - 16), (bh - 1, sl - 32)]:
+        qh, kh, vh = (t[h:h + 1].cpu().numpy() for t in (q, k, v))
+        ref, lref = O.attention_f64_rows(qh, kh, vh, r0, r0 + 32, causal, 0, scale, float(sc[4]))
+        check(o[h:h + 1, r0:r0 + 32].double().cpu().numpy(), ref,
+              lse[h:h + 1, r0:r0 + 32].double().cpu().numpy(), lref)
+    # size-independent property over every row: softmax weights sum to one, so with V replaced by the code of 1.0
+    # every output element is v_descale (here 1) whatever Q and K hold
+    v.fill_(0x38)
+    fa_ctx.ForwardEx(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 0, bh, sl, hd, causal, 0,
+                     1.0 / math.sqrt(hd), 1.0, scales.data_ptr(), scales.data_ptr() + 8, 0)
+    torch.cuda.synchronize()
+    fa_ctx.DeviceStatus()
+    assert (o.float() - 1.0).abs().max().item() <= 2e-3

@@ -281,3 +281,73 @@ def test_tile_pairs_equal_single_tiles_in_every_mode(cuda, built_libs):
     rms = float(np.sqrt(np.mean(ref ** 2)))
     maxabs, meanrel = O.error_stats(got / rms, ref / rms)
     assert maxabs <= 2e-2 and meanrel <= 1e-2, (maxabs, meanrel)
+
+
+def _device_codes(shape, seed, std=0.5):
+    """Seeded e4m3 codes generated on the device (Philox); the same bytes are copied back for the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * std).to(torch.float8_e4m3fn)
+
+
+# the shapes the headline numbers are quoted on (8192^3, 16384^3: 256-row tile pairs, 64 / 128 k-blocks through the
+# three-stage ring), the shape the one-wave-of-pairs rule exists for (4096 x 4096 x 8192), and pair counts just above a
+# multiple of the SM count (150 and 297 pairs on 148 SMs), where single tiles must be chosen instead
+@pytest.mark.parametrize("M,N,K", [(8192, 8192, 8192), (16384, 16384, 16384), (4096, 4096, 8192), (2560, 3840, 8192),
+                                   (6912, 2816, 2048), (1024, 1024, 1024), (2048, 2048, 2048)])
+def test_headline_and_sweep_shapes_on_sampled_rows(cuda, built_libs, M, N, K):
+    from goml_b200 import fp8_gemm as G
+    a, b = _device_codes((M, K), 100 + M), _device_codes((N, K), 200 + N)
+    s = torch.tensor([0.02, 0.5], device="cuda")
+    alpha = float(np.float32(0.02) * np.float32(0.5))
+
+    def run():
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4, G.OutBF16, 0)
+        torch.cuda.synchronize()
+        assert G.device_status() == 0
+        return c
+
+    c = run()
+    assert torch.isfinite(c).all()
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, M - 129, M - 128, M - 1],
+                                     np.random.default_rng(M + N).integers(0, M, 32)]))
+    ah, bh = a.view(torch.uint8)[torch.from_numpy(rows).cuda()].cpu().numpy(), b.view(torch.uint8).cpu().numpy()
+    check(c[torch.from_numpy(rows).cuda()].double().cpu().numpy(), O.gemm_f64(ah, bh, alpha), True)
+    # single tiles give the same bits whichever way the default went
+    G.SetTilePairs(0)
+    try:
+        c1 = run()
+    finally:
+        G.SetTilePairs(-1)
+    assert torch.equal(c.view(torch.int16), c1.view(torch.int16))
+    # size-independent: a checksum over every element — column sums of C equal (sum of A's rows) . B^T
+    colsum = c.double().sum(0).cpu().numpy()
+    a_sum = O.e4m3_decode(a.view(torch.uint8).cpu().numpy()).astype(np.float64).sum(0)
+    want = (O.e4m3_decode(bh).astype(np.float64) @ a_sum) * alpha
+    # each bf16 element carries a rounding error of std ~2.3e-3 |c| with random sign: six standard deviations of the sum
+    # (a missing 128-row tile would be off by ~128 r_elem, a hundred times the bound)
+    r_elem = float(c.double().pow(2).mean().sqrt().item())
+    assert np.abs(colsum - want).max() <= 1.4e-2 * np.sqrt(M) * r_elem
+
+
+@pytest.mark.parametrize("M", [16, 128])
+def test_skinny_shapes_in_full(cuda, built_libs, M):
+    # M in {16, 128}, N = K = 8192: HBM-bound shapes of the sweep (narrow tiles, two k-blocks per stage, 32 stages deep;
+    # split over K in accumulate mode), every element against the oracle
+    from goml_b200 import fp8_gemm as G
+    N = K = 8192
+    a, b = _device_codes((M, K), 300 + M), _device_codes((N, K), 301 + M)
+    s = torch.tensor([0.03, 0.25], device="cuda")
+    alpha = float(np.float32(0.03) * np.float32(0.25))
+    ref = O.gemm_f64(a.view(torch.uint8).cpu().numpy(), b.view(torch.uint8).cpu().numpy(), alpha)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4, G.OutBF16, 0)
+    x0 = torch.randn(M, N, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    x = x0.clone()
+    G.FP8GEMMAccumulateF32(M, N, K, a.data_ptr(), b.data_ptr(), x.data_ptr(), 1.0, s.data_ptr(), s.data_ptr() + 4)
+    torch.cuda.synchronize()
+    assert G.device_status() == 0
+    check(c.double().cpu().numpy(), ref, True)
+    rms = float(np.sqrt(np.mean(ref ** 2)))
+    err = np.abs(x.double().cpu().numpy() - (x0.double().cpu().numpy() + ref)).max()
+    assert err <= 1e-5 * max(rms, 1.0) * np.sqrt(K), err
