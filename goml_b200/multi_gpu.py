@@ -64,6 +64,23 @@ def allgather_rows(local_c, M: int, world_size: int, rank: int, group=None):
     return torch.cat([out[r][: spans[r][1] - spans[r][0]] for r in range(world_size)], dim=0)
 
 
+def allgather_rows_into(full_c, local_c, M: int, world_size: int, rank: int, group=None):
+    """The same exchange into a caller-owned [M, N] matrix, with no staging when the row blocks are equal
+    (M a multiple of world_size * 128, the usual case): one NCCL all-gather writes every rank's block straight
+    to its place in `full_c`.  Unequal blocks fall back to the padded exchange of ``allgather_rows``.  Returns `full_c`."""
+    import torch.distributed as dist
+
+    spans = [shard_rows(M, world_size, r) for r in range(world_size)]
+    rows = spans[0][1] - spans[0][0]
+    if all(e - b == rows for b, e in spans) and rows * world_size == M and local_c.is_contiguous() and full_c.is_contiguous():
+        if local_c.shape[0] != rows:
+            raise ValueError("local block does not match this rank's row span")
+        dist.all_gather_into_tensor(full_c, local_c, group=group)
+        return full_c
+    full_c.copy_(allgather_rows(local_c, M, world_size, rank, group))
+    return full_c
+
+
 @dataclass
 class DeviceContext:
     """Per-GPU state: device index, a CUDA stream and an FA context created on it."""

@@ -45,6 +45,14 @@ def _worker(rank, ws, port, M, N, K, q):
     r0, r1 = MG.shard_rows(M, ws, rank)
     local = torch.from_numpy(O.gemm_f64(a[r0:r1], b)).to(torch.bfloat16)  # rank-local rows, replicated B
     full = MG.allgather_rows(local, M, ws, rank)
+    into = MG.allgather_rows_into(torch.empty((M, N), dtype=torch.bfloat16), local, M, ws, rank)    # unequal blocks: padded path
+    assert torch.equal(into, full)
+    M2 = 512                                                                                       # equal blocks: one direct all-gather
+    a2, b2 = O.harness_gemm_inputs(M2, N, K)
+    s0, s1 = MG.shard_rows(M2, ws, rank)
+    local2 = torch.from_numpy(O.gemm_f64(a2[s0:s1], b2)).to(torch.bfloat16)
+    full2 = MG.allgather_rows_into(torch.empty((M2, N), dtype=torch.bfloat16), local2, M2, ws, rank)
+    assert torch.equal(full2, torch.from_numpy(O.gemm_f64(a2, b2)).to(torch.bfloat16))
     h0, h1 = MG.shard_heads(6, ws, rank)
     qa, ka, va = O.harness_attention_inputs(6, 64, 64)
     o_local, _ = O.attention_f64(qa[h0:h1], ka[h0:h1], va[h0:h1])  # heads are independent: no exchange
