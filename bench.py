@@ -70,51 +70,73 @@ def measured_peaks():
 # --------------------------------------------------------------------------- clocks
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks / throttle reasons every 50 ms.  The sampler is started ahead of the region of
+    interest (nvidia-smi takes a few hundred ms to deliver its first line); mark() opens the region, stop() closes
+    it and summarises the samples that arrived inside it.  A region shorter than the sampling period can end up with
+    no sample of its own: the summary then uses the samples taken under the same load just before it and says so."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
-        self.lines = []
+        self.lines = []      # (arrival time, text)
+        self.t_mark = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def wait_first_sample(self, timeout=3.0):
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout:
+            time.sleep(0.02)
+
+    def mark(self):
+        self.t_mark = time.time()
 
     def stop(self):
+        t_end = time.time()
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)     # one more sampling period, so that a sample taken at the end of the region arrives
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+
+        def parse(rows):
+            sm, mx, reasons = [], [], set()
+            for _, ln in rows:
+                f = [x.strip() for x in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            return sm, mx, reasons
+
+        t0 = self.t_mark if self.t_mark is not None else 0.0
+        inside = [r for r in self.lines if t0 <= r[0] <= t_end + 0.06]
+        sm, mx, reasons = parse(inside)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
         return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
@@ -337,16 +359,17 @@ def main():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters
 
+    sampler = ClockSampler(local).start()
+    sampler.wait_first_sample()
     for _ in range(args.warmup):
         if do_attn: attn()
         if do_gemm: gemm()
     torch.cuda.synchronize()
 
-    sampler = ClockSampler(local)
-    sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
     torch.cuda.synchronize()
+    sampler.mark()
     t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     t_start.record(stream)
     for i in range(args.steps):
@@ -357,9 +380,20 @@ def main():
         ev[i][2].record(stream)
     t_end.record(stream)
     torch.cuda.synchronize()
+    total_ms = t_start.elapsed_time(t_end)
+    clock_window = "timed region"
+    if total_ms < 300.0:
+        # the region is shorter than a few sampling periods: keep the identical launches going (untimed) for 0.3 s
+        # so that the clock record describes this load and not an idle gap
+        clock_window = "timed region + 0.3 s of the same launches right after it (region shorter than the sampling period)"
+        t_extra = time.time()
+        while time.time() - t_extra < 0.3:
+            if do_attn: attn()
+            if do_gemm: gemm()
+            torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    total_ms = t_start.elapsed_time(t_end)
+    clocks["window"] = clock_window
     attn_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev) if do_attn else 0.0
     gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev) if do_gemm else 0.0
     ctx.DeviceStatus()
@@ -376,9 +410,10 @@ def main():
             if (name == "attention" and not do_attn) or (name == "gemm" and not do_gemm):
                 continue
             iters = max(10, int(args.sustain_s * 1e3 / max(ms, 1e-3)) + 1)
-            smp = ClockSampler(local)
+            smp = ClockSampler(local).start()
+            smp.wait_first_sample()
             barrier()
-            smp.start()
+            smp.mark()
             t_ms = timed(fn, iters)
             ck = smp.stop()
             (t_ms,) = max_over_ranks([t_ms])
