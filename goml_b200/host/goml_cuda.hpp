@@ -191,6 +191,8 @@ struct FaLib {
     decltype(&fa_dispatch_select) dispatch = nullptr;
     decltype(&fa_kernel_name) kernel_name = nullptr;
     decltype(&fa_device_status) device_status = nullptr;
+    decltype(&fa_forward_noalloc) forward_noalloc = nullptr;
+    decltype(&fa_noalloc_device_status) noalloc_status = nullptr;
 };
 inline FaLib& fa_lib() {
     static FaLib f;
@@ -224,6 +226,8 @@ inline FaLib& fa_lib() {
         f.dispatch = sym<decltype(f.dispatch)>(f.lib, "fa_dispatch_select");
         f.kernel_name = sym<decltype(f.kernel_name)>(f.lib, "fa_kernel_name");
         f.device_status = sym<decltype(f.device_status)>(f.lib, "fa_device_status");
+        f.forward_noalloc = sym<decltype(f.forward_noalloc)>(f.lib, "fa_forward_noalloc");
+        f.noalloc_status = sym<decltype(f.noalloc_status)>(f.lib, "fa_noalloc_device_status");
     });
     if (!f.lib) throw Error(err);
     return f;
@@ -295,6 +299,17 @@ private:
     }
     fa_ctx_t* ptr_;
 };
+
+// Attention forward for callers that may not allocate (a process whose device memory map is frozen after start-up, code
+// inside a framework that reserved the whole GPU): no context, scratch in a fixed 32 MiB array inside the library, so
+// batch_heads * seq_len * head_dim <= 16 Mi per call.  Calls that overlap on the GPU share that array: one stream.
+inline void FAForwardNoAlloc(const fa_forward_args_t& a) {
+    char msg[256] = {0};
+    const FAStatus st = detail::fa_lib().forward_noalloc(&a, msg, (int)sizeof(msg));
+    if (st != FA_OK) throw Error(std::string("fa_forward_noalloc: ") + detail::fa_lib().status_str(st) + " (" + msg + ")");
+}
+// fa_device_status for callers without a context: 0, a kernel's wait-expiry code, or a negated CUDA error.
+inline int FANoAllocDeviceStatus() { return detail::fa_lib().noalloc_status(); }
 
 // ----------------------------------------------------------------------------------- quantiser
 namespace detail {
@@ -410,6 +425,79 @@ inline void ResidualAdd(uintptr_t x, uintptr_t yBF16, size_t n, uintptr_t stream
 inline void DecodeRopeAppend(const fp8_decode_append_args_t& a) {
     detail::block_check("fp8_decode_rope_append", detail::block_lib().decode_append(&a));
 }
+
+// ------------------------------------------------------------------------------- nn dispatch
+// The FP8 path of goml's nn call sites — Linear.Forward (nn/linear.go:53-74), FeedForward.forwardSwiGLU
+// (nn/feedforward.go:54-79), MultiHeadAttention.Forward (nn/attention.go:60-160) — on raw device buffers, and the
+// Llama-style block built from them (the sequence of internal/abjexam/llama_hf_f64ref.go:94-178 with every GEMM and
+// the attention in FP8).  The C++ twin of go/nn/fp8_dispatch.go, call for call.
+namespace nn {
+
+// e4m3 codes with their per-tensor scale and amax (one float each, on the device)
+struct FP8Tensor { uintptr_t codes = 0, scale = 0, amax = 0; };
+
+struct FP8Linear {   // weight [out, in], quantised once (scale = amax/448)
+    int in = 0, out = 0;
+    FP8Tensor w;
+    // y (bf16 [M, out]) = x W^T
+    void Forward(const FP8Tensor& x, int M, uintptr_t y, uintptr_t stream) const {
+        FP8GEMMScaled(M, out, in, x.codes, w.codes, y, 1.0f, x.scale, w.scale, 1 /* bf16 */, stream);
+    }
+    // h (fp32 [M, out]) += x W^T, added in the GEMM epilogue
+    void AccumulateInto(const FP8Tensor& x, int M, uintptr_t h, uintptr_t stream) const {
+        FP8GEMMAccumulateF32(M, out, in, x.codes, w.codes, h, 1.0f, x.scale, w.scale, stream);
+    }
+};
+
+// O = softmax(Q K^T / sqrt(hd)) V on per-tensor quantised Q, K, V [B*H, S, hd]; `scales` points at three device floats
+// (Q, K, V) written by the quantiser, so nothing returns to the host in between and O is in real units.
+inline void FP8Attention(FAContext& fa, uintptr_t q, uintptr_t k, uintptr_t v, uintptr_t o, uintptr_t lse, uintptr_t scales,
+                         int bh, int sl, int hd, bool causal, uintptr_t stream) {
+    fa_forward_args_t a{};
+    a.q = detail::vp(q); a.k = detail::vp(k); a.v = detail::vp(v); a.o = detail::vp(o); a.l_out = detail::vp(lse);
+    a.batch_heads = bh; a.seq_len = sl; a.head_dim = hd; a.causal = causal ? 1 : 0; a.window = 0;
+    a.scale = 1.0f / std::sqrt((float)hd); a.v_descale = 1.0f;
+    a.scale_q_dev = detail::tp<const float>(scales); a.scale_k_dev = detail::tp<const float>(scales + 4); a.scale_v_dev = detail::tp<const float>(scales + 8);
+    a.stream = reinterpret_cast<fa_stream_t>(stream);
+    fa.ForwardEx(a);
+}
+
+struct BlockBuffers {          // device buffers of one prefill pass; allocated once per shape by the caller
+    uintptr_t rstd = 0;        // fp32 [T]
+    FP8Tensor xq, oq, hq;      // [T, d], [T, d], [T, F]
+    uintptr_t qkv = 0;         // bf16 [T, 3, H, hd]
+    uintptr_t qc = 0, kc = 0, vc = 0;          // e4m3 [B*H, S, hd]
+    uintptr_t qkv_scales = 0, qkv_amax = 0;    // 3 floats each
+    uintptr_t o = 0;           // fp16 [B*H, S, hd]
+    uintptr_t hb = 0;          // bf16 [T, F]
+    uintptr_t cos = 0, sin = 0;                // fp32 [S, hd/2], from RopeTable
+};
+
+struct FP8DecoderBlock {
+    int d = 0, H = 0, F = 0;
+    float eps = 1e-5f;
+    FP8Linear qkv, o, down;
+    FP8Tensor gate_up_interleaved;   // [2*Fp, d] in the layout InterleaveGateUp produces
+    uintptr_t norm1 = 0, norm2 = 0;  // fp32 [d]
+    FAContext* fa = nullptr;
+
+    // updates the fp32 residual stream h [B*S, d] in place: ten library calls, no host synchronisation
+    void Forward(uintptr_t h, int B, int S, BlockBuffers& w, uintptr_t stream) const {
+        const int T = B * S, hd = d / H;
+        RMSNormQuantize(h, 0, 0, norm1, w.xq.codes, w.xq.scale, w.xq.amax, w.rstd, T, d, eps, stream);
+        qkv.Forward(w.xq, T, w.qkv, stream);
+        RopeQuantizeQKV(w.qkv, w.cos, w.sin, w.qc, w.kc, w.vc, w.qkv_scales, w.qkv_amax, B, S, H, hd, stream);
+        FP8Attention(*fa, w.qc, w.kc, w.vc, w.o, 0, w.qkv_scales, B * H, S, hd, true, stream);
+        PermuteQuantizeHeads(w.o, w.oq.codes, w.oq.scale, w.oq.amax, B, S, H, hd, stream);
+        o.AccumulateInto(w.oq, T, h, stream);                      // h += attention projection
+        RMSNormQuantize(h, 0, 0, norm2, w.xq.codes, w.xq.scale, w.xq.amax, w.rstd, T, d, eps, stream);
+        FP8GEMMSwiGLU(T, F, d, w.xq.codes, gate_up_interleaved.codes, w.hb, 1.0f, w.xq.scale, gate_up_interleaved.scale, w.hq.amax, stream);
+        QuantizeBF16(w.hb, w.hq.codes, w.hq.scale, w.hq.amax, (size_t)T * F, stream);
+        down.AccumulateInto(w.hq, T, h, stream);                   // h += feed-forward output
+    }
+};
+
+}  // namespace nn
 
 // --------------------------------------------------------------------------- multi-GPU manager
 // goml's Backend is single-device (backend/cuda/cuda..go:27,67).  The path shards with no exchange step:

@@ -274,8 +274,69 @@ static int run_gpu() {
     return fails;
 }
 
+// "block <dir> B S d H F": the FP8 decoder block through goml::cuda::nn, fed from files written by the Python test
+// (x, weights and norm gains as raw fp32); writes the updated residual stream to <dir>/y.f32.
+static std::vector<float> read_f32(const std::string& path, size_t n) {
+    std::vector<float> v(n);
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (!f || std::fread(v.data(), 4, n, f) != n) throw std::runtime_error("cannot read " + path);
+    std::fclose(f);
+    return v;
+}
+static int run_block(const std::string& dir, int B, int S, int d, int H, int F) {
+    namespace N = goml::cuda::nn;
+    const int T = B * S, hd = d / H, Fp = (F + 31) / 32 * 32;
+    auto fa = FAContext::FACreate();
+    // weights: upload fp32, quantise on the device with the library's quantiser (scale = amax/448)
+    struct W { DevBuf<float> f; DevBuf<uint8_t> q; DevBuf<float> sa; W(size_t n) : f(n), q(n), sa(2) {} };
+    auto load = [&](const char* name, size_t n) {
+        auto w = std::unique_ptr<W>(new W(n));
+        w->f.up(read_f32(dir + "/" + name, n));
+        QuantizeF32ToF8E4M3(w->f.addr(), w->q.addr(), w->sa.addr(), w->sa.addr() + 4, n, 0);
+        return w;
+    };
+    auto wqkv = load("wqkv.f32", (size_t)3 * d * d), wo = load("wo.f32", (size_t)d * d);
+    auto wgu = load("wgate_up.f32", (size_t)2 * F * d), wdn = load("wdown.f32", (size_t)d * F);
+    cudaDeviceSynchronize();
+    DevBuf<uint8_t> wgui((size_t)2 * Fp * d);
+    wgui.up(InterleaveGateUp(wgu->q.down(), F, d));
+    DevBuf<float> g1(d), g2(d), h((size_t)T * d);
+    g1.up(read_f32(dir + "/g1.f32", d)); g2.up(read_f32(dir + "/g2.f32", d)); h.up(read_f32(dir + "/x.f32", (size_t)T * d));
+    // work buffers
+    DevBuf<float> rstd(T), sx(2), so(2), sh(2), s3(6), cosb((size_t)S * hd / 2), sinb((size_t)S * hd / 2);
+    DevBuf<uint8_t> xq((size_t)T * d), oq((size_t)T * d), hq((size_t)T * F), qc((size_t)T * d), kc((size_t)T * d), vc((size_t)T * d);
+    DevBuf<uint16_t> qkv((size_t)T * 3 * d), o16((size_t)T * d), hb((size_t)T * F);
+    RopeTable(cosb.addr(), sinb.addr(), S, hd, 10000.0f, 0);
+    N::FP8DecoderBlock blk;
+    blk.d = d; blk.H = H; blk.F = F; blk.eps = 1e-5f; blk.fa = fa.get();
+    blk.qkv = {d, 3 * d, {wqkv->q.addr(), wqkv->sa.addr(), wqkv->sa.addr() + 4}};
+    blk.o = {d, d, {wo->q.addr(), wo->sa.addr(), wo->sa.addr() + 4}};
+    blk.down = {F, d, {wdn->q.addr(), wdn->sa.addr(), wdn->sa.addr() + 4}};
+    blk.gate_up_interleaved = {wgui.addr(), wgu->sa.addr(), wgu->sa.addr() + 4};
+    blk.norm1 = g1.addr(); blk.norm2 = g2.addr();
+    N::BlockBuffers w;
+    w.rstd = rstd.addr();
+    w.xq = {xq.addr(), sx.addr(), sx.addr() + 4}; w.oq = {oq.addr(), so.addr(), so.addr() + 4}; w.hq = {hq.addr(), sh.addr(), sh.addr() + 4};
+    w.qkv = qkv.addr(); w.qc = qc.addr(); w.kc = kc.addr(); w.vc = vc.addr();
+    w.qkv_scales = s3.addr(); w.qkv_amax = s3.addr() + 12; w.o = o16.addr(); w.hb = hb.addr(); w.cos = cosb.addr(); w.sin = sinb.addr();
+    blk.Forward(h.addr(), B, S, w, 0);
+    cudaDeviceSynchronize();
+    fa->DeviceStatus();
+    CHECK(FP8GEMMDeviceStatus() == 0);
+    auto y = h.down();
+    FILE* f = std::fopen((dir + "/y.f32").c_str(), "wb");
+    if (!f || std::fwrite(y.data(), 4, y.size(), f) != y.size()) throw std::runtime_error("cannot write y.f32");
+    std::fclose(f);
+    return fails;
+}
+
 int main(int argc, char** argv) {
     try {
+        if (argc >= 8 && !std::strcmp(argv[1], "block")) {
+            int f = run_block(argv[2], std::atoi(argv[3]), std::atoi(argv[4]), std::atoi(argv[5]), std::atoi(argv[6]), std::atoi(argv[7]));
+            std::printf("%s\n", f ? "FAILED" : "block ok");
+            return f != 0;
+        }
         if (argc >= 3 && !std::strcmp(argv[1], "cpu")) { int f = run_cpu(argv[2]); std::printf("%s\n", f ? "FAILED" : "cpu ok"); return f != 0; }
         if (argc >= 2 && !std::strcmp(argv[1], "gpu")) { int f = run_gpu(); std::printf("%s\n", f ? "FAILED" : "gpu ok"); return f != 0; }
     } catch (const std::exception& e) {

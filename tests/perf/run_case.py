@@ -1,14 +1,14 @@
 """Run one kernel of the path a few times on cuda:0 (for profilers and quick checks).
 
-    python -m goml_b200.run_case fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
-    python -m goml_b200.run_case gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
-    python -m goml_b200.run_case blockdec B S D_MODEL H F ITERS  # one decode step of the whole FP8 block against a cache of S keys
-    python -m goml_b200.run_case decstep B HQ HKV S D ITERS    # new token's RoPE + quantise + cache append, then fa_decode
-    python -m goml_b200.run_case gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
-    python -m goml_b200.run_case quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
-    python -m goml_b200.run_case glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
-    python -m goml_b200.run_case decode B HQ HKV S D ITERS [PAGE]   # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing; PAGE: paged cache
-    python -m goml_b200.run_case block B S D H F ITERS         # one fused FP8 decoder block (goml_b200.nn), random-init weights
+    python tests/perf/run_case.py fa   BH S D CAUSAL ITERS      # fa_forward_train, random e4m3 inputs
+    python tests/perf/run_case.py gemm M N K ITERS              # fp8_gemm_scaled, bf16 out
+    python tests/perf/run_case.py blockdec B S D_MODEL H F ITERS  # one decode step of the whole FP8 block against a cache of S keys
+    python tests/perf/run_case.py decstep B HQ HKV S D ITERS    # new token's RoPE + quantise + cache append, then fa_decode
+    python tests/perf/run_case.py gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
+    python tests/perf/run_case.py quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
+    python tests/perf/run_case.py glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
+    python tests/perf/run_case.py decode B HQ HKV S D ITERS [PAGE]   # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing; PAGE: paged cache
+    python tests/perf/run_case.py block B S D H F ITERS         # one fused FP8 decoder block (goml_b200.nn), random-init weights
 
 torch only allocates the device buffers; every launch goes through the C ABI.
 """
@@ -17,7 +17,10 @@ import sys
 
 import torch
 
-from . import block_glue as BG, fa_forward as F, fp8_gemm as G, quantize as Q
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from goml_b200 import block_glue as BG, fa_forward as F, fp8_gemm as G, quantize as Q  # noqa: E402
 
 
 def main(argv):
@@ -76,7 +79,7 @@ def main(argv):
             Q.QuantizeF32ToF8E4M3(x.data_ptr(), q.data_ptr(), s.data_ptr(), s.data_ptr() + 4, n, 0)
         torch.cuda.synchronize()
     elif kind == "block":
-        from . import nn
+        from goml_b200 import nn
         B, S, d, H, Fh, iters = args
         g = torch.Generator(device="cuda").manual_seed(4)
         rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device="cuda") * std
@@ -126,7 +129,7 @@ def main(argv):
         print(f"decode B={B} Hq={hq} Hkv={hkv} S={S} D={D}{f' page={page}' if page else ''}: {us:8.1f} us   {nbytes / us / 1e3:7.0f} GB/s of the KV cache ({nbytes / 1e6:.0f} MB)")
     elif kind == "blockdec":
         # one decode step of the whole block (one new token per sequence) against a cache of S keys per sequence
-        from . import nn
+        from goml_b200 import nn
         B, S, d, H, Fh, iters = args
         g = torch.Generator(device="cuda").manual_seed(4)
         rn = lambda *shape, std=0.02: torch.randn(*shape, generator=g, device="cuda") * std
@@ -178,7 +181,7 @@ def main(argv):
         blk.close()
     elif kind == "decstep":
         # one decode step's attention part: RoPE + quantise + cache append of the new token, then fa_decode
-        from . import block_glue as BG
+        from goml_b200 import block_glue as BG
         B, hq, hkv, S, D, iters = args
         ctx = F.FACreate()
         g = torch.Generator(device="cuda").manual_seed(0)

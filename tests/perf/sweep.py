@@ -1,6 +1,6 @@
 """Shape sweep of the FP8 attention forward and the FP8 GEMM on cuda:0 (CUDA-event timing).
 
-    python -m goml_b200.sweep [attn] [gemm]
+    python tests/perf/sweep.py [attn] [gemm]
 
 Attention: hd in {64,128}, S in {1024,4096,16384,32768}, H=32, B chosen so that B*S = 65536, causal and
 non-causal.  GEMM: squares 1024..16384 and skinny M in {16,128} with N=K=8192, bf16 output.
@@ -11,7 +11,10 @@ import sys
 
 import torch
 
-from . import fa_forward as F, fp8_gemm as G
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from goml_b200 import fa_forward as F, fp8_gemm as G  # noqa: E402
 
 
 def _time(fn, iters, warm=3):

@@ -143,3 +143,22 @@ def test_product_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text and "liboracle" not in text, f
+
+
+def test_build_script_builds_and_honours_target_only(tmp_path):
+    # goml_b200/build_cuda.sh is the counterpart of the reference's scripts/build_cuda.sh for these libraries; unlike
+    # that script (scripts/build_cuda.sh:67-87 never reads the variable its Makefile:24-32 exports) it honours
+    # GOML_TARGET_ONLY, and refuses a target list without sm_100a
+    script = os.path.join(ROOT, "goml_b200", "build_cuda.sh")
+    if not shutil.which("nvcc"):
+        pytest.skip("nvcc not available")
+    env = dict(os.environ, LIBS_DIR=str(tmp_path))
+    r = subprocess.run(["bash", script, "quant"], env=env, capture_output=True, text=True)
+    assert r.returncode == 0 and (tmp_path / "libfp8quant.so").exists(), r.stdout + r.stderr
+    assert "arch=compute_100a,code=sm_100a" in r.stdout
+    env["GOML_TARGET_ONLY"] = "-gencode arch=compute_89,code=sm_89"
+    r = subprocess.run(["bash", script, "quant"], env=env, capture_output=True, text=True)
+    assert r.returncode == 2 and "sm_100a-only" in r.stderr
+    env["GOML_TARGET_ONLY"] = "-gencode arch=compute_100a,code=sm_100a"
+    r = subprocess.run(["bash", script, "nosuchtarget"], env=env, capture_output=True, text=True)
+    assert r.returncode == 2
