@@ -196,7 +196,7 @@ def reference_cpu_run(steps: int, warmup: int, cores: int | None = None):
     return {"value": tflops, "unit": "TFLOPS", "cores": cores, "kind": kind, "sample": sample}, dt / steps * 1e3
 
 
-def run_reference_arm(args):
+def run_reference_arm(args, emit=print):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
@@ -211,7 +211,7 @@ def run_reference_arm(args):
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
     return 0
 
 
@@ -256,7 +256,22 @@ def numa_bind(dev_index: int) -> dict:
     return info
 
 
+def _json_only_stdout():
+    """Libraries (NCCL's version banner, for one) print to the process's stdout; the contract is ONE JSON line there.
+    File descriptor 1 is pointed at stderr for the run and the returned writer emits the line on the real stdout."""
+    real = os.dup(1)
+    sys.stdout.flush()
+    os.dup2(2, 1)
+
+    def emit(text: str) -> None:
+        sys.stdout.flush()
+        os.write(real, (text + "\n").encode())
+
+    return emit
+
+
 def main():
+    emit = _json_only_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -275,7 +290,7 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
-        return run_reference_arm(args)
+        return run_reference_arm(args, emit)
 
     import torch
     import torch.distributed as dist
@@ -588,7 +603,7 @@ def main():
         base, _ = reference_cpu_run(steps=4, warmup=1)
         line["cpu_baseline"] = base
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     ctx.Destroy()
     if world > 1:
         dist.destroy_process_group()
