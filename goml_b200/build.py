@@ -23,7 +23,7 @@ NVCC_FLAGS = [
 
 # library file -> sources
 TARGETS = {
-    "libfp8gemm.so": ["fp8_gemm_sm100.cu"],
+    "libfp8gemm.so": ["fp8_gemm_sm100.cu", "fp8_gemm_mx_sm100.cu"],
     "libfa_sm120.so": ["fa_api.cu", "fa_fwd_sm100.cu", "fa_decode_sm100.cu", "fa_dispatch.cpp"],
     "libfp8quant.so": ["fp8_quantize_sm100.cu"],
     "libfp8block.so": ["fp8_block_glue_sm100.cu"],

@@ -50,7 +50,7 @@ build() {   # output, sources...
 }
 
 TARGET="${1:-all}"
-case "$TARGET" in all|fp8gemm) build libfp8gemm.so fp8_gemm_sm100.cu ;; esac
+case "$TARGET" in all|fp8gemm) build libfp8gemm.so fp8_gemm_sm100.cu fp8_gemm_mx_sm100.cu ;; esac
 case "$TARGET" in all|fa)      build libfa_sm120.so fa_api.cu fa_fwd_sm100.cu fa_decode_sm100.cu fa_dispatch.cpp ;; esac
 case "$TARGET" in all|quant)   build libfp8quant.so fp8_quantize_sm100.cu ;; esac
 case "$TARGET" in all|block)   build libfp8block.so fp8_block_glue_sm100.cu ;; esac

@@ -156,6 +156,47 @@ __global__ void __launch_bounds__(THREADS) quant_fp16_kernel(const __half* __res
     }
 }
 
+// ---- block-scaled ("MXFP8") quantiser: one ue8m0 scale per 32 consecutive elements of a row (OCP microscaling:
+// scale = 2^(floor(log2(amax)) - 8), 8 = the largest e4m3 exponent; elements = e4m3_rn_satfinite(x / scale)).
+// One thread per block of 32: 128 bytes read, 32 codes and one scale byte written; the scale byte goes to the tiled
+// position the block-scaled GEMM copies from (fp8_gemm.h: fp8_gemm_mx).
+__global__ void __launch_bounds__(THREADS) quant_mx_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                           int rows, int K) {
+    const int kblocks = K / 32;
+    const size_t total = (size_t)rows * kblocks;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int row = (int)(i / kblocks), kb = (int)(i - (size_t)row * kblocks);
+        const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * K + kb * 32);
+        float4 v[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            v[j] = __ldg(src + j);
+            amax = fmaxf(fmaxf(amax, fabsf(v[j].x)), fmaxf(fabsf(v[j].y), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));  // NaN never wins
+        }
+        int se = 0;                                   // an all-zero block keeps scale 1
+        if (amax > 0.f && amax <= 3.4028234e38f) se = ilogbf(amax) - 8;
+        else if (amax > 3.4028234e38f) se = 127;      // infinity in the block
+        se = max(-127, min(127, se));
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            // x * 2^-se is exact (a change of exponent) unless the result is subnormal in fp32
+            const float a = fminf(fmaxf(scalbnf(v[j].x, -se), -448.f), 448.f), b = fminf(fmaxf(scalbnf(v[j].y, -se), -448.f), 448.f);
+            const float c = fminf(fmaxf(scalbnf(v[j].z, -se), -448.f), 448.f), d = fminf(fmaxf(scalbnf(v[j].w, -se), -448.f), 448.f);
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+            w[j] = lo | (hi << 16);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(q + (size_t)row * K + kb * 32);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        const size_t chunk = (size_t)(row >> 7) * (K / 128) + (kb >> 2);
+        sf[chunk * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kb & 3)] = (uint8_t)(se + 127);
+    }
+}
+
 int grid_for(size_t work_items) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -201,5 +242,18 @@ int fp8_quantize_fp16(const void* input_fp16, void* output_fp8, float* scale_out
 }
 
 int cuda_device_sync2(void) { return (int)cudaDeviceSynchronize(); }
+
+int fp8_quantize_mx_f32(const float* x, uint8_t* q, uint8_t* scales, int rows, int K, void* stream) {
+    if (!x || !q || !scales || rows < 0 || K <= 0 || (K % 128) != 0) return (int)cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15)) return (int)cudaErrorInvalidValue;
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    // entries of the padding rows of the last 128-row tile: scale 1 (never the NaN byte)
+    const size_t sf_bytes = (size_t)((rows + 127) / 128) * (size_t)(K / 128) * 512;
+    cudaError_t e = cudaMemsetAsync(scales, 0x7f, sf_bytes, s);
+    if (e != cudaSuccess) return (int)e;
+    quant_mx_kernel<<<grid_for((size_t)rows * (K / 32)), THREADS, 0, s>>>(x, q, scales, rows, K);
+    return (int)cudaGetLastError();
+}
 
 }  // extern "C"

@@ -49,6 +49,11 @@ def _init():
                 lib.fp8_gemm_fp8out.restype = i
                 lib.fp8_gemm_fp8out.argtypes = [i, i, i, p, p, p, f, p, p, p, p, p]
                 lib.fp8_gemm_device_status.restype = i
+                lib.fp8_gemm_mx.restype = i
+                lib.fp8_gemm_mx.argtypes = [i, i, i, p, p, p, p, p, f, i, p]
+                lib.fp8_mx_scale_bytes.restype = C.c_size_t
+                lib.fp8_mx_scale_bytes.argtypes = [i, i]
+                lib.fp8_gemm_mx_device_status.restype = i
                 lib.fp8_gemm_selftest_wait_expiry.restype = i
                 lib.fp8_gemm_selftest_wait_expiry.argtypes = [p]
                 lib.fp8_gemm_set_tile_pairs.restype = i
@@ -137,6 +142,18 @@ def SetTilePairs(mode: int) -> None:
     rc = _init().fp8_gemm_set_tile_pairs(mode)
     if rc != 0:
         raise FP8GEMMError(f"fp8_gemm_set_tile_pairs: CUDA error {rc}")
+
+
+def FP8GEMMMX(M, N, K, A, scale_a, B, scale_b, Cptr, alpha=1.0, out_dtype=OutBF16, stream=0) -> None:
+    """Block-scaled GEMM: e4m3 codes with one ue8m0 scale per 32 K elements of every row of A and of B (the arrays
+    fp8_quantize_mx_f32 writes); C = alpha * sum_kb 2^(ea+eb) A_kb . B_kb, fp32 accumulation, fp16/bf16 out."""
+    rc = _init().fp8_gemm_mx(M, N, K, A, scale_a, B, scale_b, Cptr, alpha, out_dtype, stream or None)
+    if rc != 0:
+        raise FP8GEMMError(f"fp8_gemm_mx: CUDA error {rc}")
+
+
+def mx_device_status() -> int:
+    return _init().fp8_gemm_mx_device_status()
 
 
 def SelftestWaitExpiry(stream: int = 0) -> None:

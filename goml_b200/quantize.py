@@ -37,6 +37,8 @@ def _init():
             lib.fp8_quantize_fp16.restype = C.c_int
             lib.fp8_quantize_fp16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
             lib.cuda_device_sync2.restype = C.c_int
+            lib.fp8_quantize_mx_f32.restype = C.c_int
+            lib.fp8_quantize_mx_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
             _lib = lib
     return _lib
 
@@ -70,3 +72,15 @@ def DeviceSync2() -> None:
     rc = _init().cuda_device_sync2()
     if rc != 0:
         raise QuantizeError(f"cuda_device_sync2: CUDA error {rc}")
+
+
+def mx_scale_bytes(rows: int, K: int) -> int:
+    """Size of the tiled ue8m0 scale array of a [rows, K] block-scaled tensor (one scale per 32 elements along K)."""
+    return ((rows + 127) // 128) * ((K + 127) // 128) * 512
+
+
+def QuantizeMXF32(src: int, codes: int, scales: int, rows: int, K: int, stream: int = 0) -> None:
+    """[rows, K] fp32 -> e4m3 codes + ue8m0 block scales (fp8_quantize_mx_f32), the operand format of FP8GEMMMX."""
+    rc = _init().fp8_quantize_mx_f32(src, codes, scales, rows, K, stream or None)
+    if rc != 0:
+        raise QuantizeError(f"fp8_quantize_mx_f32: CUDA error {rc}")

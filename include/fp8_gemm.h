@@ -24,6 +24,8 @@
 #ifndef GOML_FP8_GEMM_H_
 #define GOML_FP8_GEMM_H_
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -89,6 +91,23 @@ FP8GEMM_API int fp8_gemm_swiglu(int M, int F, int K, const void* A, const void* 
 FP8GEMM_API int fp8_gemm_fp8out(int M, int N, int K, const void* A, const void* B, void* D, float alpha,
                                 const float* scale_a, const float* scale_b, const float* scale_d, float* amax_d,
                                 void* stream);
+
+/* Additive, no counterpart in the reference (its roadmap's next step, docs/FP8_FA_ROADMAP.md:137-148): the block-scaled
+ * ("MXFP8") GEMM.  A and B are e4m3 codes as before; every row of A and of B carries one ue8m0 scale (a power of two,
+ * byte = exponent + 127, 0xFF is NaN) per 32 consecutive K elements, and
+ *   C[m,n] = alpha * sum over K blocks kb of 2^(ea[m,kb] + eb[n,kb]) * (A[m, 32 kb .. 32 kb + 31] . B[n, 32 kb .. 32 kb + 31]),
+ * the scales applied inside the tensor-core instruction (tcgen05.mma kind::mxf8f6f4.block_scale), fp32 accumulation,
+ * FP16 or BF16 output.  K must be a multiple of 128.
+ * Scale arrays (scale_a for the M rows of A, scale_b for the N rows of B) are device arrays of fp8_mx_scale_bytes(rows, K)
+ * bytes in the order the kernel copies them: for row tile rt = row / 128 and slab ks = kb / 4 the 512 bytes at
+ * (rt * (K / 128) + ks) * 512 hold, at byte ((row % 32) * 16 + ((row % 128) / 32) * 4 + kb % 4), the scale of (row, kb);
+ * entries of rows past the matrix must not be 0xFF.  fp8_quantize_mx_f32 (libfp8quant.so) writes codes and scales in
+ * this form.  A, B, scale_a, scale_b 16-byte aligned. */
+FP8GEMM_API size_t fp8_mx_scale_bytes(int rows, int K);
+FP8GEMM_API int fp8_gemm_mx(int M, int N, int K, const void* A, const void* scale_a, const void* B, const void* scale_b, void* C,
+                            float alpha, int out_dtype, void* stream);
+/* Bounded-wait status of the block-scaled kernel (as fp8_gemm_device_status). */
+FP8GEMM_API int fp8_gemm_mx_device_status(void);
 
 /* Additive: tile-pair policy of this process.  mode -1 = chosen per problem (default), 0 = large problems run as
  * single 128 x 256 tiles instead of 256-row tile pairs; other values return cudaErrorInvalidValue.  Results are

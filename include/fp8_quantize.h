@@ -58,6 +58,14 @@ FP8QUANT_API int fp8_dequantize_to_fp16(const void* input_fp8, void* output_fp16
  * bit-identical to the reference's. */
 FP8QUANT_API int fp8_quantize_fp16(const void* input_fp16, void* output_fp8, float* scale_out, int n);
 
+/* Additive, no counterpart in the reference: the block-scaled ("MXFP8", OCP microscaling) quantiser that feeds
+ * fp8_gemm_mx (libfp8gemm.so).  x is [rows, K] fp32 row-major, K a multiple of 128.  For every 32 consecutive elements
+ * of a row: scale = 2^(floor(log2(amax)) - 8) (1 for an all-zero block), stored as ue8m0 (exponent + 127), and codes =
+ * e4m3_rn_satfinite(x / scale) (values up to 2^9 occur before the conversion; those above 448 saturate, as the format
+ * specifies).  q receives rows * K codes; scales receives ceil(rows / 128) * (K / 128) * 512 bytes in the tiled order
+ * fp8_gemm_mx reads (include/fp8_gemm.h), padding entries set to scale 1.  x and q 16-byte aligned. */
+FP8QUANT_API int fp8_quantize_mx_f32(const float* x, uint8_t* q, uint8_t* scales, int rows, int K, void* stream);
+
 /* Replaces cuda_device_sync2 (libs1/fp8_quantize_v2.cu:216): cudaDeviceSynchronize() as int. */
 FP8QUANT_API int cuda_device_sync2(void);
 

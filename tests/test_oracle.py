@@ -136,3 +136,30 @@ def test_output_rounding_helpers():
     a = O.seeded_normal("t", (4, 5), config="c")
     assert np.array_equal(a, O.seeded_normal("t", (4, 5), config="c"))
     assert not np.array_equal(a, O.seeded_normal("u", (4, 5), config="c"))
+
+
+def test_mx_restatement_properties():
+    # block-scaled format: scales are the OCP shared exponents, elements stay within e4m3 range, dequantisation error is
+    # bounded by half an e4m3 step of the block's largest element, and the tiled scale order is a permutation
+    import numpy as np
+    from oracle import mx
+    x = (O.seeded_normal("x", (130, 256), config="mxcpu") * np.exp2(np.arange(256) // 32 - 4)[None, :]).astype(np.float32)
+    x[3, :32] = 0
+    codes, scales = mx.quantize_mx(x)
+    assert codes.shape == x.shape and scales.shape == (130, 8) and scales[3, 0] == 127
+    amax = np.abs(x).reshape(130, 8, 32).max(-1)
+    nz = amax > 0
+    assert np.all(np.exp2(scales.astype(int) - 127 + 8)[nz] <= amax[nz]) and np.all(amax[nz] < np.exp2(scales.astype(int) - 127 + 9)[nz])
+    back = mx.dequantize_mx(codes, scales)
+    err = np.abs(back - x).reshape(130, 8, 32).max(-1)
+    # scaled elements reach [256, 512): half an e4m3 step there is 16, and what lies above 448 saturates (error < 64)
+    assert np.all(err <= np.exp2(scales.astype(float) - 127) * 64) and np.median(err / np.exp2(scales.astype(float) - 127)) <= 16
+    tiled = mx.tile_scales(scales, 256)
+    assert tiled.size == 2 * 2 * 512
+    assert tiled[(0 * 2 + 1) * 512 + 5 * 16 + 2 * 4 + 3] == scales[2 * 32 + 5, 4 + 3]     # row 69, block 7
+    assert tiled[(1 * 2 + 0) * 512 + 1 * 16 + 0 * 4 + 0] == scales[129, 0] and tiled[(1 * 2 + 0) * 512 + 9 * 16] == 0x7F   # padding rows
+    a, sa = mx.quantize_mx(O.seeded_normal("a", (4, 64), config="mxcpu"))
+    b, sb = mx.quantize_mx(O.seeded_normal("b", (3, 64), config="mxcpu"))
+    want = sum(np.ldexp(O.e4m3_decode(a[:, 32 * k:32 * k + 32]).astype(np.float64) @ O.e4m3_decode(b[:, 32 * k:32 * k + 32]).astype(np.float64).T,
+                        (sa[:, k].astype(int)[:, None] - 127) + (sb[:, k].astype(int)[None, :] - 127)) for k in range(2))
+    assert np.allclose(mx.gemm_mx_f64(a, sa, b, sb), want, rtol=1e-13)
