@@ -26,6 +26,8 @@ var fp8gemmB200 struct {
 	fp8out   func(M, N, K int32, A, B, D uintptr, alpha float32, scaleA, scaleB, scaleD, amaxD, stream uintptr) int32
 	status   func() int32
 	setPairs func(mode int32) int32
+	mx       func(M, N, K int32, A, scaleA, B, scaleB, C uintptr, alpha float32, outDType int32, stream uintptr) int32
+	mxBytes  func(rows, K int32) uintptr
 }
 
 func initFP8GEMMB200() error {
@@ -45,6 +47,8 @@ func initFP8GEMMB200() error {
 		purego.RegisterLibFunc(&fp8gemmB200.fp8out, lib, "fp8_gemm_fp8out")
 		purego.RegisterLibFunc(&fp8gemmB200.status, lib, "fp8_gemm_device_status")
 		purego.RegisterLibFunc(&fp8gemmB200.setPairs, lib, "fp8_gemm_set_tile_pairs")
+		purego.RegisterLibFunc(&fp8gemmB200.mx, lib, "fp8_gemm_mx")
+		purego.RegisterLibFunc(&fp8gemmB200.mxBytes, lib, "fp8_mx_scale_bytes")
 	})
 	return fp8gemmB200.err
 }
@@ -129,4 +133,24 @@ func FP8GEMMSetTilePairs(mode int) error {
 		return fmt.Errorf("fp8_gemm_set_tile_pairs: CUDA error %d", rc)
 	}
 	return nil
+}
+
+// FP8GEMMMX: the block-scaled ("MXFP8") GEMM — e4m3 codes with one ue8m0 scale per 32 K elements of every row of A and
+// of B (the arrays QuantizeMXF32 writes); C = alpha * sum over blocks of 2^(ea+eb) * A_kb . B_kb.  K % 128 == 0.
+func FP8GEMMMX(M, N, K int, A, scaleA, B, scaleB, C uintptr, alpha float32, outDType int, stream uintptr) error {
+	if err := initFP8GEMMB200(); err != nil {
+		return err
+	}
+	if rc := fp8gemmB200.mx(int32(M), int32(N), int32(K), A, scaleA, B, scaleB, C, alpha, int32(outDType), stream); rc != 0 {
+		return fmt.Errorf("fp8_gemm_mx: CUDA error %d", rc)
+	}
+	return nil
+}
+
+// MXScaleBytes: size of the tiled scale array of a [rows, K] block-scaled tensor.
+func MXScaleBytes(rows, K int) (int, error) {
+	if err := initFP8GEMMB200(); err != nil {
+		return 0, err
+	}
+	return int(fp8gemmB200.mxBytes(int32(rows), int32(K))), nil
 }

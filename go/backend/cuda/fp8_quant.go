@@ -25,6 +25,7 @@ var fp8quant struct {
 	quantFP16 func(x, q, scaleOut uintptr, n int32) int32
 	dequant   func(q, out, scaleIn uintptr, n int32) int32
 	sync2     func() int32
+	quantMX   func(x, q, scales uintptr, rows, K int32, stream uintptr) int32
 }
 
 func initFP8Quant() error {
@@ -38,6 +39,7 @@ func initFP8Quant() error {
 		purego.RegisterLibFunc(&fp8quant.quantFP16, lib, "fp8_quantize_fp16")
 		purego.RegisterLibFunc(&fp8quant.dequant, lib, "fp8_dequantize_to_fp16")
 		purego.RegisterLibFunc(&fp8quant.sync2, lib, "cuda_device_sync2")
+		purego.RegisterLibFunc(&fp8quant.quantMX, lib, "fp8_quantize_mx_f32")
 	})
 	return fp8quant.err
 }
@@ -91,6 +93,18 @@ func DeviceSync2() error {
 	}
 	if rc := fp8quant.sync2(); rc != 0 {
 		return fmt.Errorf("cuda_device_sync2: CUDA error %d", rc)
+	}
+	return nil
+}
+
+// QuantizeMXF32: [rows, K] fp32 -> e4m3 codes + ue8m0 block scales (one per 32 elements along K), the operand format
+// of FP8GEMMMX; scales receives MXScaleBytes(rows, K) bytes.
+func QuantizeMXF32(src, codes, scales uintptr, rows, K int, stream uintptr) error {
+	if err := initFP8Quant(); err != nil {
+		return err
+	}
+	if rc := fp8quant.quantMX(src, codes, scales, int32(rows), int32(K), stream); rc != 0 {
+		return fmt.Errorf("fp8_quantize_mx_f32: CUDA error %d", rc)
 	}
 	return nil
 }

@@ -63,6 +63,11 @@ def build_all(force: bool = False, verbose: bool = False, only: list[str] | None
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {lib}:\n{r.stdout}\n{r.stderr}")
         built.append(out)
+    # north_star names the attention library by the glob libflash_attention*.so: the FP8 forward is reachable under
+    # that family name too
+    alias = os.path.join(LIBS, "libflash_attention_fp8.so")
+    if os.path.exists(os.path.join(LIBS, "libfa_sm120.so")) and not os.path.lexists(alias):
+        os.symlink("libfa_sm120.so", alias)
     return built
 
 

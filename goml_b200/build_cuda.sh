@@ -51,7 +51,8 @@ build() {   # output, sources...
 
 TARGET="${1:-all}"
 case "$TARGET" in all|fp8gemm) build libfp8gemm.so fp8_gemm_sm100.cu fp8_gemm_mx_sm100.cu ;; esac
-case "$TARGET" in all|fa)      build libfa_sm120.so fa_api.cu fa_fwd_sm100.cu fa_decode_sm100.cu fa_dispatch.cpp ;; esac
+case "$TARGET" in all|fa)      build libfa_sm120.so fa_api.cu fa_fwd_sm100.cu fa_decode_sm100.cu fa_dispatch.cpp
+                               ln -sf libfa_sm120.so "$LIBS_DIR/libflash_attention_fp8.so" ;; esac   # reachable under the libflash_attention*.so family name too
 case "$TARGET" in all|quant)   build libfp8quant.so fp8_quantize_sm100.cu ;; esac
 case "$TARGET" in all|block)   build libfp8block.so fp8_block_glue_sm100.cu ;; esac
 case "$TARGET" in all|fp8gemm|fa|quant|block) ;; *) echo "unknown target '$TARGET'" >&2; exit 2 ;; esac

@@ -96,6 +96,9 @@ struct GemmLib {
     int (*swiglu)(int, int, int, const void*, const void*, void*, float, const float*, const float*, float*, void*) = nullptr;
     int (*fp8out)(int, int, int, const void*, const void*, void*, float, const float*, const float*, const float*, float*, void*) = nullptr;
     int (*status)() = nullptr;
+    int (*mx)(int, int, int, const void*, const void*, const void*, const void*, void*, float, int, void*) = nullptr;
+    size_t (*mx_scale_bytes)(int, int) = nullptr;
+    int (*set_pairs)(int) = nullptr;
 };
 inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
     static GemmLib g;
@@ -112,6 +115,9 @@ inline GemmLib& gemm_lib() {  // sync.Once-style (fp8_gemm.go:27-41)
         g.swiglu = sym<decltype(g.swiglu)>(g.lib, "fp8_gemm_swiglu");
         g.fp8out = sym<decltype(g.fp8out)>(g.lib, "fp8_gemm_fp8out");
         g.status = sym<decltype(g.status)>(g.lib, "fp8_gemm_device_status");
+        g.mx = sym<decltype(g.mx)>(g.lib, "fp8_gemm_mx");
+        g.mx_scale_bytes = sym<decltype(g.mx_scale_bytes)>(g.lib, "fp8_mx_scale_bytes");
+        g.set_pairs = sym<decltype(g.set_pairs)>(g.lib, "fp8_gemm_set_tile_pairs");
     });
     if (!g.lib) throw Error(err);
     return g;
@@ -172,6 +178,21 @@ inline std::vector<uint8_t> InterleaveGateUp(const std::vector<uint8_t>& gateUp,
     return out;
 }
 inline int FP8GEMMDeviceStatus() { return detail::gemm_lib().status(); }
+
+// Block-scaled ("MXFP8") GEMM: e4m3 codes with one ue8m0 scale per 32 K elements of every row of A and of B (the arrays
+// QuantizeMXF32 writes); C = alpha * sum over blocks of 2^(ea + eb) * A_kb . B_kb, fp16 / bf16 out.  K % 128 == 0.
+inline void FP8GEMMMX(int M, int N, int K, uintptr_t A, uintptr_t scaleA, uintptr_t B, uintptr_t scaleB, uintptr_t C, float alpha,
+                      int outDType, uintptr_t stream) {
+    const int rc = detail::gemm_lib().mx(M, N, K, detail::vp(A), detail::vp(scaleA), detail::vp(B), detail::vp(scaleB), detail::vp(C), alpha,
+                                         outDType, detail::vp(stream));
+    if (rc != 0) throw Error("fp8_gemm_mx: CUDA error " + std::to_string(rc));
+}
+inline size_t MXScaleBytes(int rows, int K) { return detail::gemm_lib().mx_scale_bytes(rows, K); }
+// -1 = tile pairs chosen per problem (default), 0 = single tiles only (bit-identical results)
+inline void FP8GEMMSetTilePairs(int mode) {
+    const int rc = detail::gemm_lib().set_pairs(mode);
+    if (rc != 0) throw Error("fp8_gemm_set_tile_pairs: CUDA error " + std::to_string(rc));
+}
 
 // ----------------------------------------------------------------------------------- attention
 using FAStatus = fa_status_t;
@@ -316,6 +337,8 @@ namespace detail {
 struct QuantLib {
     void* lib = nullptr;
     int (*quant)(const float*, uint8_t*, float*, float*, size_t, int, void*) = nullptr;
+    int (*quant_fp16)(const void*, void*, float*, int) = nullptr;
+    int (*quant_mx)(const float*, uint8_t*, uint8_t*, int, int, void*) = nullptr;
 };
 inline QuantLib& quant_lib() {
     static QuantLib q;
@@ -325,6 +348,8 @@ inline QuantLib& quant_lib() {
         q.lib = dlopen(resolveLib("libfp8quant.so").c_str(), RTLD_LAZY);
         if (!q.lib) { err = std::string("fp8quant: dlopen: ") + dlerror(); return; }
         q.quant = sym<decltype(q.quant)>(q.lib, "fp8_quantize_f32");
+        q.quant_fp16 = sym<decltype(q.quant_fp16)>(q.lib, "fp8_quantize_fp16");
+        q.quant_mx = sym<decltype(q.quant_mx)>(q.lib, "fp8_quantize_mx_f32");
     });
     if (!q.lib) throw Error(err);
     return q;
@@ -342,6 +367,18 @@ inline void QuantizeF32ToF8E4M3(uintptr_t src, uintptr_t dst, uintptr_t scale, u
 // scale = amax: decoded magnitudes <= 1 (battle_a_llm.go:476)
 inline void QuantizeF32ToF8E4M3Unit(uintptr_t src, uintptr_t dst, uintptr_t scale, uintptr_t amax, size_t n, uintptr_t stream = 0) {
     detail::quantize(src, dst, scale, amax, n, 1, stream);
+}
+
+// fp8_quantize_fp16 of libs1/fp8_quantize_v2.cu:176-204: FP16 source, scale = amax/448, legacy default stream
+inline void QuantizeFP16(uintptr_t src, uintptr_t dst, uintptr_t scale, int n) {
+    const int rc = detail::quant_lib().quant_fp16(detail::vp(src), detail::vp(dst), reinterpret_cast<float*>(scale), n);
+    if (rc != 0) throw Error("fp8_quantize_fp16: CUDA error " + std::to_string(rc));
+}
+// [rows, K] fp32 -> e4m3 codes + ue8m0 block scales (one per 32 elements), the operand format of FP8GEMMMX
+inline void QuantizeMXF32(uintptr_t src, uintptr_t codes, uintptr_t scales, int rows, int K, uintptr_t stream = 0) {
+    const int rc = detail::quant_lib().quant_mx(reinterpret_cast<const float*>(src), reinterpret_cast<uint8_t*>(codes),
+                                                reinterpret_cast<uint8_t*>(scales), rows, K, detail::vp(stream));
+    if (rc != 0) throw Error("fp8_quantize_mx_f32: CUDA error " + std::to_string(rc));
 }
 
 // ----------------------------------------------------------------------- decoder-block glue

@@ -5,6 +5,7 @@
     python tests/perf/run_case.py blockdec B S D_MODEL H F ITERS  # one decode step of the whole FP8 block against a cache of S keys
     python tests/perf/run_case.py decstep B HQ HKV S D ITERS    # new token's RoPE + quantise + cache append, then fa_decode
     python tests/perf/run_case.py gemm8 M N K ITERS             # bf16-out and e4m3-out epilogues timed side by side
+    python tests/perf/run_case.py gemm_mx M N K ITERS           # block-scaled GEMM (fp8_gemm_mx) beside the per-tensor kernel, with timing
     python tests/perf/run_case.py quant N ITERS                 # fp8_quantize_f32 (scale = amax/448)
     python tests/perf/run_case.py glue B S D H F ITERS          # the six libfp8block.so ops of one decoder block, with timings
     python tests/perf/run_case.py decode B HQ HKV S D ITERS [PAGE]   # fa_decode: one token per sequence, e4m3 KV cache of S keys, with timing; PAGE: paged cache
@@ -45,6 +46,32 @@ def main(argv):
             G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, 0, 0, G.OutBF16, 0)
         torch.cuda.synchronize()
         assert G.device_status() == 0
+    elif kind == "gemm_mx":
+        M, N, K, iters = args
+        xa, xb = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda")
+        a, b = torch.empty(M, K, dtype=torch.uint8, device="cuda"), torch.empty(N, K, dtype=torch.uint8, device="cuda")
+        sa = torch.empty(Q.mx_scale_bytes(M, K), dtype=torch.uint8, device="cuda")
+        sb = torch.empty(Q.mx_scale_bytes(N, K), dtype=torch.uint8, device="cuda")
+        Q.QuantizeMXF32(xa.data_ptr(), a.data_ptr(), sa.data_ptr(), M, K)
+        Q.QuantizeMXF32(xb.data_ptr(), b.data_ptr(), sb.data_ptr(), N, K)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        runs = {
+            "block-scaled (fp8_gemm_mx)": lambda: G.FP8GEMMMX(M, N, K, a.data_ptr(), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), c.data_ptr(), 1.0, G.OutBF16),
+            "per-tensor (fp8_gemm_scaled)": lambda: G.FP8GEMMScaled(M, N, K, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1.0, 0, 0, G.OutBF16, 0),
+        }
+        for name, fn in runs.items():
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            print(f"{name}: {M}x{N}x{K}  {ms * 1e3:.1f} us  {2.0 * M * N * K / ms / 1e9:.0f} TFLOPS")
+        assert G.mx_device_status() == 0 and G.device_status() == 0
     elif kind == "gemm8":
         # the e4m3-output epilogue beside the bf16 one on the same operands: ms and TFLOPS of each
         M, N, K, iters = args

@@ -162,3 +162,14 @@ def test_build_script_builds_and_honours_target_only(tmp_path):
     env["GOML_TARGET_ONLY"] = "-gencode arch=compute_100a,code=sm_100a"
     r = subprocess.run(["bash", script, "nosuchtarget"], env=env, capture_output=True, text=True)
     assert r.returncode == 2
+
+
+def test_family_name_alias_loads_the_same_library(built_libs):
+    # libflash_attention_fp8.so is an alias of libfa_sm120.so for callers that look the attention library up by the
+    # libflash_attention*.so family name
+    import ctypes
+    alias = os.path.join(built_libs, "libflash_attention_fp8.so")
+    assert os.path.islink(alias) and os.readlink(alias) == "libfa_sm120.so"
+    lib = ctypes.CDLL(alias)
+    lib.fa_version.restype = ctypes.c_char_p
+    assert b"sm100a" in lib.fa_version()
