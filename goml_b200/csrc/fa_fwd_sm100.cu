@@ -52,6 +52,7 @@ constexpr int BM = 128;  // query rows per CTA (= TMEM lanes)
 constexpr int BN = 64;   // keys per block
 constexpr int STAGES = 3; // K / V shared-memory ring depth
 constexpr int NUM_SOFTMAX_WARPS = 4;   // one thread per query row
+constexpr int HEAD_GROUP = 16;         // heads whose tiles are interleaved when tiles differ in length (48 MB of K/V at S = 8192, D = 128)
 constexpr int NUM_THREADS = (NUM_SOFTMAX_WARPS + 2) * 32;
 constexpr int MMA_WARP = NUM_SOFTMAX_WARPS;
 constexpr int TMA_WARP = NUM_SOFTMAX_WARPS + 1;
@@ -179,9 +180,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // tile -> (head, query tile); within a head the tiles with the most keys come first
-    const int head = blockIdx.x / p.n_qtiles;
-    const int qt = p.n_qtiles - 1 - (blockIdx.x % p.n_qtiles);
+    // tile -> (head, query tile).  Tiles of equal cost go head by head, so that the CTAs in
+    // flight share a few heads' K/V in L2.  When the key range depends on the query tile
+    // (causal, window) the heads are taken in groups of HEAD_GROUP, and inside a group the
+    // tiles with the most keys come first across all its heads: the last CTAs of the launch
+    // are then the short tiles of a whole group, not the long tiles of the last head.
+    int head, qt;
+    if (p.causal || p.window > 0) {
+        const int per_group = HEAD_GROUP * p.n_qtiles;
+        const int g = blockIdx.x / per_group;
+        const int r = blockIdx.x - g * per_group;
+        const int heads_here = min(HEAD_GROUP, p.bh - g * HEAD_GROUP);
+        head = g * HEAD_GROUP + r % heads_here;
+        qt = p.n_qtiles - 1 - r / heads_here;
+    } else {
+        head = blockIdx.x / p.n_qtiles;
+        qt = p.n_qtiles - 1 - (blockIdx.x % p.n_qtiles);
+    }
     const int q0 = qt * BM;
     // keys this tile can see: [kv_lo, kv_hi)
     const int kv_hi = p.causal ? min(p.sl, q0 + BM) : p.sl;

@@ -109,6 +109,17 @@ __device__ __forceinline__ void wait_expiry_selftest_body(uint32_t* device_statu
     }
 }
 
+// One lane of a converged warp (all 32 lanes must execute this).  A single-thread role (TMA producer, MMA issuer)
+// runs its loop on the whole warp and predicates only the issuing instructions with this: the loop's addresses and
+// descriptors then stay warp-uniform and the compiler keeps them in uniform registers, where tcgen05 / TMA
+// instructions read their operands.  The same loop inside `if (lane == 0)` is divergent code: every operand of every
+// issue goes through a vector-to-uniform register move first, which measured about twice the issue time per MMA.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
