@@ -232,31 +232,42 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         // fall through to teardown
     } else if (warp == TMA_WARP) {
         // ------------------------------------------------------------- TMA producer
-        if (lane == 0) {
-            prefetch_tmap(&tmap_q);
-            prefetch_tmap(&tmap_k);
-            prefetch_tmap(&tmap_v);
-            mbar_arrive_expect_tx(bar_q, C::Q_BYTES);
-            tma_load_3d(sbase + C::OFF_Q, &tmap_q, bar_q, 0, q0, head);
+        // The whole warp runs the loop and one elected lane issues: addresses and coordinates stay warp-uniform.
+        {
+            const bool leader = elect_one();
+            if (leader) {
+                prefetch_tmap(&tmap_q);
+                prefetch_tmap(&tmap_k);
+                prefetch_tmap(&tmap_v);
+                mbar_arrive_expect_tx(bar_q, C::Q_BYTES);
+                tma_load_3d(sbase + C::OFF_Q, &tmap_q, bar_q, 0, q0, head);
+            }
             int s = 0;
             uint32_t ph = 1;  // "previous phase complete": the rings start empty
             for (int j = 0; j < nblk; j++) {
                 const int key0 = (blk0 + j) * BN;
                 if (!mbar_wait(bar_sfull + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;   // Q K^T three blocks back is done
-                mbar_arrive_expect_tx(bar_kfull + 8 * s, C::K_BYTES);
-                tma_load_3d(sbase + C::OFF_K + s * C::K_BYTES, &tmap_k, bar_kfull + 8 * s, 0, key0, head);
+                if (leader) {
+                    mbar_arrive_expect_tx(bar_kfull + 8 * s, C::K_BYTES);
+                    tma_load_3d(sbase + C::OFF_K + s * C::K_BYTES, &tmap_k, bar_kfull + 8 * s, 0, key0, head);
+                }
                 if (!mbar_wait(bar_pvdone + 8 * s, ph, abort_flag, ST_TIMEOUT_LOAD)) break;  // P V three blocks back is done
-                mbar_arrive_expect_tx(bar_vfull + 8 * s, C::V_BYTES);
+                if (leader) {
+                    mbar_arrive_expect_tx(bar_vfull + 8 * s, C::V_BYTES);
 #pragma unroll
-                for (int h = 0; h < HD / 64; h++)  // one 64-column (128-byte) slab of d per copy
-                    tma_load_3d(sbase + C::OFF_V + s * C::V_BYTES + h * C::V_HALF_BYTES, &tmap_v, bar_vfull + 8 * s,
-                                h * 64, key0, head);
+                    for (int h = 0; h < HD / 64; h++)  // one 64-column (128-byte) slab of d per copy
+                        tma_load_3d(sbase + C::OFF_V + s * C::V_BYTES + h * C::V_HALF_BYTES, &tmap_v, bar_vfull + 8 * s,
+                                    h * 64, key0, head);
+                }
+                __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
         }
     } else if (warp == MMA_WARP) {
         // -------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // Whole warp, one elected lane issues (descriptors stay in uniform registers).
+        {
+            const bool leader = elect_one();
             constexpr uint32_t idesc_qk = make_idesc_e4m3_f32(BM, BN, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_f16_f32(BM, HD, 0, 1);  // A = P from TMEM, V is MN-major
             auto qk_desc = [&](uint32_t addr) { return HD == 128 ? kmajor_desc_sw128(addr) : kmajor_desc_sw64(addr); };
@@ -270,10 +281,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 tc_fence_after();
                 const uint64_t qd = qk_desc(sbase + C::OFF_Q);
                 const uint64_t kd = qk_desc(sbase + C::OFF_K + ks * C::K_BYTES);
+                if (leader) {
 #pragma unroll
-                for (int k = 0; k < HD / 32; k++)
-                    mma_f8f6f4_ss(tmem_s + (j & 1) * BN, qd + 2 * k, kd + 2 * k, idesc_qk, k != 0);
-                mma_commit(bar_sfull + 8 * ks);
+                    for (int k = 0; k < HD / 32; k++)
+                        mma_f8f6f4_ss(tmem_s + (j & 1) * BN, qd + 2 * k, kd + 2 * k, idesc_qk, k != 0);
+                    mma_commit(bar_sfull + 8 * ks);
+                }
+                __syncwarp();
                 if (++ks == STAGES) { ks = 0; kph ^= 1; }
             };
             ok = mbar_wait(bar_q, 0, abort_flag, ST_TIMEOUT_MMA);
@@ -285,12 +299,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t vaddr = sbase + C::OFF_V + vs * C::V_BYTES;
+                if (leader) {
 #pragma unroll
-                for (int k = 0; k < BN / 16; k++) {  // 16 keys per MMA: 8 TMEM columns of P, 16 rows of V
-                    const uint64_t vd = mnmajor_desc_sw128(vaddr + k * 16 * 128, C::V_HALF_BYTES);
-                    mma_f16_ts(tmem_o, tmem_s + b * BN + 8 * k, vd, idesc_pv, (j | k) != 0);
+                    for (int k = 0; k < BN / 16; k++) {  // 16 keys per MMA: 8 TMEM columns of P, 16 rows of V
+                        const uint64_t vd = mnmajor_desc_sw128(vaddr + k * 16 * 128, C::V_HALF_BYTES);
+                        mma_f16_ts(tmem_o, tmem_s + b * BN + 8 * k, vd, idesc_pv, (j | k) != 0);
+                    }
+                    mma_commit(bar_pvdone + 8 * vs);
                 }
-                mma_commit(bar_pvdone + 8 * vs);
+                __syncwarp();
                 if (++vs == STAGES) { vs = 0; vph ^= 1; }
                 // S[b] is rewritten by the Q K^T two blocks ahead; it is issued behind this P V on the
                 // same in-order tensor pipe, so P(j) has been read before S(j+2) lands on it
