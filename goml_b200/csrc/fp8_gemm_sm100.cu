@@ -201,7 +201,9 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop and one elected lane issues: coordinates and addresses stay warp-uniform.
+        {
+            const bool leader = elect_one();
             int stage = 0;
             uint32_t phase = 1;  // "previous phase complete": the ring starts empty
             bool ok = true;
@@ -213,23 +215,28 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (int ks = ks0; ks < ks1; ks++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     const uint32_t fb = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(fb, KSUB * (MT * p.a_rows * BK + bn * BK));
+                    if (leader) {
+                        mbar_arrive_expect_tx(fb, KSUB * (MT * p.a_rows * BK + bn * BK));
 #pragma unroll
-                    for (int sub = 0; sub < KSUB; sub++) {
-                        // a k-block past the end of K (odd count) is a fully out-of-range box: zero-filled, bytes still counted
-                        const int kb = ks * KSUB + sub;
-                        const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
-                        tma_load_2d(sa, &tmap_a, fb, kb * BK, MT * tm * BM);
-                        if (MT == 2) tma_load_2d(sa + A_BYTES, &tmap_a, fb, kb * BK, (2 * tm + 1) * BM);   // past M: zero-filled
-                        tma_load_2d(sa + MT * A_BYTES, tb, fb, kb * BK, n0);
+                        for (int sub = 0; sub < KSUB; sub++) {
+                            // a k-block past the end of K (odd count) is a fully out-of-range box: zero-filled, bytes still counted
+                            const int kb = ks * KSUB + sub;
+                            const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * SUB_BYTES;
+                            tma_load_2d(sa, &tmap_a, fb, kb * BK, MT * tm * BM);
+                            if (MT == 2) tma_load_2d(sa + A_BYTES, &tmap_a, fb, kb * BK, (2 * tm + 1) * BM);   // past M: zero-filled
+                            tma_load_2d(sa + MT * A_BYTES, tb, fb, kb * BK, n0);
+                        }
                     }
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // Whole warp, one elected lane issues (descriptors stay in uniform registers).
+        {
+            const bool leader = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             uint32_t tphase[2] = {1, 1};  // both accumulator buffers start free
@@ -255,7 +262,7 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                         for (int k = 0; k < BK / 32; k++) {
                             // +32 bytes along K inside the swizzle span = +2 in the address field
-                            mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
+                            if (leader) mma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
                         }
                         if (MT == 2) {
                             // lower half of the pair: the other accumulator buffer, the same B operand.  Its buffer is
@@ -269,15 +276,16 @@ fp8_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             const uint64_t adesc2 = kmajor_desc_sw128(sa + A_BYTES);
 #pragma unroll
                             for (int k = 0; k < BK / 32; k++)
-                                mma_f8f6f4_ss(tmem_base + BN, adesc2 + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
+                                if (leader) mma_f8f6f4_ss(tmem_base + BN, adesc2 + 2 * k, bdesc + 2 * k, idesc, ((ks - ks0) | sub | k) != 0);
                         }
                     }
                     if (!ok) break;
-                    mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
+                    if (leader) mma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs retire
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                if (ok) mma_commit(bar_tfull + 8 * buf);  // accumulator complete
-                if (ok && MT == 2) mma_commit(bar_tfull + 8);
+                if (ok && leader) mma_commit(bar_tfull + 8 * buf);  // accumulator complete
+                if (ok && leader && MT == 2) mma_commit(bar_tfull + 8);
                 buf ^= 1;
             }
         }
