@@ -178,7 +178,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
 
     // tile -> (head, query tile).  Tiles of equal cost go head by head, so that the CTAs in
     // flight share a few heads' K/V in L2.  When the key range depends on the query tile
