@@ -71,6 +71,8 @@ CASES = [
     (1, 1, 128, 0, 0), (1, 1, 64, 1, 0), (2, 17, 128, 1, 0), (3, 280, 128, 0, 0), (2, 300, 64, 1, 0),
     (1, 129, 128, 1, 0), (1, 127, 64, 0, 0), (2, 1000, 128, 1, 200), (2, 1000, 64, 0, 333),
     (1, 512, 128, 1, 1), (1, 512, 64, 1, 512), (4, 1024, 128, 0, 0), (4, 1024, 64, 1, 0), (1, 2048, 128, 1, 128),
+    # more heads than one group of the causal / window tile order (groups of 16 heads, longest tiles first), last group partial
+    (19, 300, 128, 1, 0), (37, 260, 64, 1, 50), (33, 257, 128, 0, 100),
 ]
 
 
