@@ -334,6 +334,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
 
+        // two blocks per trip: the S buffer index (j & 1) and everything derived from it become compile-time constants
+#pragma unroll 2
         for (int j = 0; j < nblk; j++) {
             const int key0 = (blk0 + j) * BN;
             const int b = j & 1;
