@@ -325,7 +325,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         float ascale = fabsf(scale_log2);
         if (ascale == 0.f) ascale = 1e-30f;      // keeps -inf * scale = -inf for masked keys
         float m_ref = -INFINITY;                 // reference max used in the exponent (log2 units)
-        float l = 0.f;                           // running sum of P * 2^POFF
+        float m_thr = -INFINITY;                 // m_ref + TAU
+        float nmsub = 0.f;                       // POFF - m_ref (0 while no finite score has been seen)
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;   // running sum of P * 2^POFF, in four partial sums
         bool ok = true;
         int rs = 0;           // ring stage of block j (j % STAGES) and its phase; those of block j-1
         uint32_t rph = 0;
@@ -333,6 +335,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         uint32_t rph_prev = 0;
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
+        const bool may_mask = p.causal || p.window > 0 || (p.sl % BN) != 0;   // else no block of this launch has a masked key
 
         // two blocks per trip: the S buffer index (j & 1) and everything derived from it become compile-time constants
 #pragma unroll 2
@@ -355,8 +358,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 for (int c = 0; c < BN; c++) sreg[c] = tmp[c];
             }
             // does this block need per-element masking?  (uniform across the CTA)
-            const bool mask_blk = (key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
-                                  (p.window > 0 && key0 < q0 + BM - p.window);
+            const bool mask_blk = may_mask && ((key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
+                                               (p.window > 0 && key0 < q0 + BM - p.window));
             if (mask_blk) {
                 // the empty volatile statement keeps this a real (in the common case not-taken) branch
                 // instead of 64 predicated selects executed for every block
@@ -378,28 +381,33 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             }
             const float mx = fmaxf(max3(max3(mxa[0], mxa[1], mxa[2]), max3(mxa[3], mxa[4], mxa[5]), mxa[6]), mxa[7]) * ascale;
 
-            const bool bump = mx > m_ref + TAU;  // true also on the first finite max
-            const float m_new = bump ? mx : m_ref;
-            if (j > 0 && __any_sync(0xffffffffu, bump)) {
-                // O is final only once the previous P V has finished
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * rs_prev, rph_prev, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
-                tc_fence_after();
-                const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
-                l *= f;
+            // The reference moves only when some row's maximum exceeds it by more than 2^TAU (always on the first finite
+            // maximum: m_thr starts at -inf); everything that depends on it is state updated in this rare branch, so the
+            // common path is one compare and one vote.
+            if (__any_sync(0xffffffffu, mx > m_thr)) {
+                const bool bump = mx > m_thr;
+                const float m_new = bump ? mx : m_ref;
+                if (j > 0) {
+                    // O is final only once the previous P V has finished
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * rs_prev, rph_prev, abort_flag, ST_TIMEOUT_SOFTMAX))) { ok = false; break; }
+                    tc_fence_after();
+                    const float f = bump ? ex2(m_ref - m_new) : 1.0f;  // m_ref = -inf -> 0
+                    l0 *= f; l1 *= f; l2 *= f; l3 *= f;
 #pragma unroll
-                for (int c = 0; c < HD / 16; c++) {
-                    uint32_t o[16];
-                    tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
-                    tmem_ld_wait();
+                    for (int c = 0; c < HD / 16; c++) {
+                        uint32_t o[16];
+                        tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tmem_st_32x32b_x16(tmem_o + lane_off + c * 16, o);
+                        for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st_32x32b_x16(tmem_o + lane_off + c * 16, o);
+                    }
                 }
+                m_ref = m_new;
+                m_thr = m_ref + TAU;
+                nmsub = (m_ref == -INFINITY) ? 0.f : POFF - m_ref;
             }
-            m_ref = m_new;
-            const float nmsub = (m_ref == -INFINITY) ? 0.f : POFF - m_ref;
 
-            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
             for (int g = 0; g < BN / 32; g++) {  // 32 keys -> 16 TMEM columns of packed fp16 pairs
                 uint32_t w[16];
@@ -415,7 +423,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
                 tmem_st_32x32b_x16(tmem_s + lane_off + b * BN + g * 16, w);  // P overwrites the first half of S[b]
             }
-            l += (l0 + l1) + (l2 + l3);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar_pfull + 8 * b);
@@ -427,6 +434,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         // epilogue: O / l (times the V dequantisation scale) -> fp16
         if (ok && __all_sync(0xffffffffu, mbar_wait(bar_pvdone + 8 * rs_prev, rph_prev, abort_flag, ST_TIMEOUT_SOFTMAX))) {
             tc_fence_after();
+            const float l = (l0 + l1) + (l2 + l3);
             const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
             const float inv = (l > 0.f) ? vds / l : 0.f;
             __half* orow = p.o + ((size_t)head * p.sl + qi) * HD;
