@@ -158,7 +158,9 @@ __device__ __noinline__ void negate_scores(uint32_t* s) {
     for (int c = 0; c < BN; c++) s[c] ^= 0x80000000u;
 }
 
-template <int HD>
+// MASKED = false: no key of the launch is masked (non-causal, no window, S a multiple of the block), and the masking code
+// is not compiled into the softmax loop at all.
+template <int HD, bool MASKED>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const Params p) {
@@ -335,7 +337,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         uint32_t rph_prev = 0;
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
-        const bool may_mask = p.causal || p.window > 0 || (p.sl % BN) != 0;   // else no block of this launch has a masked key
 
         // two blocks per trip: the S buffer index (j & 1) and everything derived from it become compile-time constants
 #pragma unroll 2
@@ -358,7 +359,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 for (int c = 0; c < BN; c++) sreg[c] = tmp[c];
             }
             // does this block need per-element masking?  (uniform across the CTA)
-            const bool mask_blk = may_mask && ((key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
+            const bool mask_blk = MASKED && ((key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
                                                (p.window > 0 && key0 < q0 + BM - p.window));
             if (mask_blk) {
                 // the empty volatile statement keeps this a real (in the common case not-taken) branch
@@ -517,7 +518,9 @@ cudaError_t launch_hd(const LaunchArgs& a, int num_sms) {
     p.lse = a.lse;
     const long long grid = (long long)a.bh * p.n_qtiles;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
-    fa_fwd_kernel<HD><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, a.stream>>>(tq, tk, tv, p);
+    const bool masked = a.causal || a.window > 0 || (a.sl % BN) != 0;
+    if (masked) fa_fwd_kernel<HD, true><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, a.stream>>>(tq, tk, tv, p);
+    else fa_fwd_kernel<HD, false><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, a.stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
 }
 
@@ -525,8 +528,10 @@ cudaError_t launch_hd(const LaunchArgs& a, int num_sms) {
 
 namespace {
 void init_device(DeviceState* st, int dev) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fwd_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<128>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fwd_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fa_fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::SMEM_BYTES);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&st->num_sms, cudaDevAttrMultiProcessorCount, dev);
     st->init_error = e;
 }
