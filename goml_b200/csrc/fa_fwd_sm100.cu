@@ -338,6 +338,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         const int hi_key = p.causal ? min(qi, p.sl - 1) : p.sl - 1;   // last visible key of this row
         const int lo_key = (p.window > 0) ? qi - p.window + 1 : 0;    // first visible key
 
+        // Blocks that need per-element masking (uniform across the CTA): those that reach past the sequence end or past the
+        // tile's first query (causal) — from j_mask_hi on — and those that start before the window of the tile's last query
+        // — below j_mask_lo.  With 64-key blocks and 128-query tiles: (blk0 + j + 1) * BN > sl  <=>  j >= sl / BN - blk0;
+        // (blk0 + j + 1) * BN - 1 > q0  <=>  j >= q0 / BN - blk0;  (blk0 + j) * BN < q0 + BM - window  <=>  j < ceil(..) - blk0.
+        int j_mask_hi = p.sl / BN - blk0;
+        if (p.causal) j_mask_hi = min(j_mask_hi, q0 / BN - blk0);
+        const int j_mask_lo = (p.window > 0 && q0 + BM - p.window > 0) ? (q0 + BM - p.window + BN - 1) / BN - blk0 : 0;
+
         // two blocks per trip: the S buffer index (j & 1) and everything derived from it become compile-time constants
 #pragma unroll 2
         for (int j = 0; j < nblk; j++) {
@@ -359,8 +367,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 for (int c = 0; c < BN; c++) sreg[c] = tmp[c];
             }
             // does this block need per-element masking?  (uniform across the CTA)
-            const bool mask_blk = MASKED && ((key0 + BN > p.sl) || (p.causal && key0 + BN - 1 > q0) ||
-                                               (p.window > 0 && key0 < q0 + BM - p.window));
+            const bool mask_blk = MASKED && (j < j_mask_lo || j >= j_mask_hi);
             if (mask_blk) {
                 // the empty volatile statement keeps this a real (in the common case not-taken) branch
                 // instead of 64 predicated selects executed for every block
