@@ -158,8 +158,9 @@ __device__ __noinline__ void negate_scores(uint32_t* s) {
     for (int c = 0; c < BN; c++) s[c] ^= 0x80000000u;
 }
 
-// MASKED = false: no key of the launch is masked (non-causal, no window, S a multiple of the block), and the masking code
-// is not compiled into the softmax loop at all.
+// MASKED = false: no key of the launch is masked (non-causal, no window, S a multiple of the block) and the host-side scale
+// is positive: neither the masking code nor the sign flip of a negative scale is compiled into the softmax loop.  (The
+// device-side scale factors are quantiser outputs, amax / 448: never negative.)
 template <int HD, bool MASKED>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -358,7 +359,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             for (int c = 0; c < BN / 32; c++) tmem_ld_32x32b_x32(tmem_s + lane_off + b * BN + c * 32, sreg + c * 32);
             tmem_ld_wait();
 
-            if (neg) {  // out of line, on a local copy so that sreg stays in registers
+            if (MASKED && neg) {  // out of line, on a local copy so that sreg stays in registers
                 uint32_t tmp[BN];
 #pragma unroll
                 for (int c = 0; c < BN; c++) tmp[c] = sreg[c];
@@ -525,7 +526,7 @@ cudaError_t launch_hd(const LaunchArgs& a, int num_sms) {
     p.lse = a.lse;
     const long long grid = (long long)a.bh * p.n_qtiles;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
-    const bool masked = a.causal || a.window > 0 || (a.sl % BN) != 0;
+    const bool masked = a.causal || a.window > 0 || (a.sl % BN) != 0 || !(a.scale > 0.f);
     if (masked) fa_fwd_kernel<HD, true><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, a.stream>>>(tq, tk, tv, p);
     else fa_fwd_kernel<HD, false><<<(unsigned)grid, NUM_THREADS, C::SMEM_BYTES, a.stream>>>(tq, tk, tv, p);
     return cudaGetLastError();
