@@ -446,22 +446,41 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const float l = (l0 + l1) + (l2 + l3);
             const float vds = p.sv ? p.v_descale * __ldg(p.sv) : p.v_descale;
             const float inv = (l > 0.f) ? vds / l : 0.f;
-            __half* orow = p.o + ((size_t)head * p.sl + qi) * HD;
+            // O leaves through shared memory so that the global stores are coalesced: a thread owns one row (HD fp16 = ROWB
+            // bytes), which written straight to global makes every store instruction of a warp touch 32 different lines.
+            // Each warp stages its 32 rows in the (by now idle) K ring — 16-byte chunk c of row r at chunk c ^ (r % CPR), so
+            // that both the row-wise writes and the read-back are free of bank conflicts — and stores them back as whole
+            // 512-byte runs.  Only this warp touches its staging area: a __syncwarp() orders the two passes.
+            constexpr int ROWB = HD * 2;            // bytes per output row
+            constexpr int CPR = ROWB / 16;          // 16-byte chunks per row: 16 (D = 128) or 8 (D = 64)
+            uint8_t* stage = smem + C::OFF_K + warp * (32 * ROWB);
+            const int lane = threadIdx.x & 31;
 #pragma unroll
             for (int c = 0; c < HD / 16; c++) {
                 uint32_t o[16];
                 tmem_ld_32x32b_x16(tmem_o + lane_off + c * 16, o);
                 tmem_ld_wait();
-                if (qi < p.sl) {
 #pragma unroll
-                    for (int v = 0; v < 2; v++) {
-                        uint4 w;
-                        w.x = pack_half2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        w.y = pack_half2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        w.z = pack_half2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        w.w = pack_half2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 16 + v * 8) = w;
-                    }
+                for (int v = 0; v < 2; v++) {
+                    uint4 w;
+                    w.x = pack_half2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                    w.y = pack_half2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                    w.z = pack_half2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                    w.w = pack_half2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                    const int ch = 2 * c + v;
+                    *reinterpret_cast<uint4*>(stage + lane * ROWB + ((ch ^ (lane % CPR)) << 4)) = w;
+                }
+            }
+            __syncwarp();
+            {
+                constexpr int RPI = 32 / CPR;       // rows per store instruction: 2 (D = 128) or 4 (D = 64)
+                uint8_t* obase = reinterpret_cast<uint8_t*>(p.o + ((size_t)head * p.sl + q0 + warp * 32) * HD);
+                const int rows_left = p.sl - (q0 + warp * 32);   // rows of this warp inside the sequence
+#pragma unroll
+                for (int i = 0; i < 32 / RPI; i++) {
+                    const int rr = i * RPI + lane / CPR, ch = lane % CPR;
+                    const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * ROWB + ((ch ^ (rr % CPR)) << 4));
+                    if (rr < rows_left) *reinterpret_cast<uint4*>(obase + (size_t)rr * ROWB + (ch << 4)) = w;
                 }
             }
             if (p.lse && qi < p.sl) {
